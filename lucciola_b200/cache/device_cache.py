@@ -13,13 +13,13 @@ from typing import Sequence
 import torch
 
 from ..parts.base import KVCacheView, KVPages, StateCacheView, StateSlot
-from .manager import CacheGroup
+from .manager import CacheGroup, flat_requests
 
 
 def bytes_per_page(groups: Sequence[CacheGroup], page_size: int, dtype: torch.dtype) -> int:
     """Bytes one page id costs when every group gets the same number of pages."""
     el = torch.empty((), dtype=dtype).element_size()
-    return sum(len(g.cache_ids) * 2 * g.num_kv_heads * page_size * g.head_dim * el for g in groups)
+    return sum(len(g.cache_ids) * (1 if g.shared else 2) * g.num_kv_heads * page_size * g.head_dim * el for g in groups)
 
 
 def pages_that_fit(groups: Sequence[CacheGroup], page_size: int, dtype: torch.dtype, device: torch.device,
@@ -36,21 +36,25 @@ class DeviceCache:
                  page_size: int, num_pages: Sequence[int], num_slots: int, dtype: torch.dtype, device: torch.device):
         self.page_size = page_size
         self.pools: list[torch.Tensor] = []
-        self.views: list[object] = [None] * len(requests)
+        single: dict[object, object] = {}
         for gi, g in enumerate(groups):
-            pool = torch.zeros((len(g.cache_ids), 2, num_pages[gi], g.num_kv_heads, page_size, g.head_dim),
+            pool = torch.zeros((len(g.cache_ids), 1 if g.shared else 2, num_pages[gi], g.num_kv_heads, page_size, g.head_dim),
                                dtype=dtype, device=device)
             self.pools.append(pool)
-            for li, cid in enumerate(g.cache_ids):
-                self.views[cid] = KVCacheView(pool[li, 0], pool[li, 1], gi, page_size)
-        self.states: dict[int, torch.Tensor] = {}
-        for cid, r in enumerate(requests):
+            for li, key in enumerate(g.cache_ids):
+                single[key] = KVCacheView(pool[li, 0], pool[li, 0 if g.shared else 1], gi, page_size)
+        self.states: dict[object, torch.Tensor] = {}
+        for key, r in flat_requests(requests):
             if isinstance(r, StateSlot):
                 # one row more than there are slots: row `num_slots` belongs to no request; the entries that pad a
                 # recorded step read and write it
                 st = torch.zeros((num_slots + 1, *r.shape), dtype=r.dtype, device=device)
-                self.states[cid] = st
-                self.views[cid] = StateCacheView(st)
+                self.states[key] = st
+                single[key] = StateCacheView(st)
+        # a cache id that asked for a tuple gets a tuple of views in the same order
+        self.views: list[object] = [
+            tuple(single.get((cid, j)) for j in range(len(r))) if isinstance(r, tuple) else single.get(cid)
+            for cid, r in enumerate(requests)]
 
     def zero_slots(self, slots: torch.Tensor, stream: int) -> None:
         """Clear the state rows of newly admitted requests.  `slots`: int32 on the device, negative entries name

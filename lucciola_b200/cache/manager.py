@@ -28,19 +28,33 @@ class CacheGroup:
     num_kv_heads: int
     head_dim: int
     window: int                      # 0: all keys
-    cache_ids: tuple[int, ...]       # the model's cache ids that live in this group
+    cache_ids: tuple                 # the model's caches that live in this group: cache ids, or (cache id, place) for a
+                                     # member of a cache id that asked for a tuple
+    shared: bool = False             # one vector a token is key and value at once
 
 
-def plan_groups(requests: Sequence[KVPages | StateSlot | None]) -> tuple[list[CacheGroup], list[int]]:
-    """Group the model's caches by their needs.  Returns the groups and the cache ids that hold state."""
-    by_key: dict[tuple[int, int, int], list[int]] = {}
-    state_ids: list[int] = []
+def flat_requests(requests: Sequence[KVPages | StateSlot | None | tuple]) -> list[tuple[object, object]]:
+    """Every single thing the model's caches hold: (key, request), the key being the cache id, or (cache id, place)
+    for the members of a cache id that asks for a tuple."""
+    out = []
     for cid, r in enumerate(requests):
+        if isinstance(r, tuple):
+            out += [((cid, j), one) for j, one in enumerate(r)]
+        else:
+            out.append((cid, r))
+    return out
+
+
+def plan_groups(requests: Sequence[KVPages | StateSlot | None | tuple]) -> tuple[list[CacheGroup], list]:
+    """Group the model's paged caches by their needs.  Returns the groups and the keys (see flat_requests) that hold state."""
+    by_key: dict[tuple, list] = {}
+    state_ids: list = []
+    for key, r in flat_requests(requests):
         if isinstance(r, KVPages):
-            by_key.setdefault((r.num_kv_heads, r.head_dim, r.window), []).append(cid)
+            by_key.setdefault((r.num_kv_heads, r.head_dim, r.window, r.shared), []).append(key)
         elif isinstance(r, StateSlot):
-            state_ids.append(cid)
-    groups = [CacheGroup(k[0], k[1], k[2], tuple(v)) for k, v in by_key.items()]
+            state_ids.append(key)
+    groups = [CacheGroup(k[0], k[1], k[2], tuple(v), k[3]) for k, v in by_key.items()]
     return groups, state_ids
 
 

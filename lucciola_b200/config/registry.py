@@ -1,6 +1,6 @@
 """One registry from the architecture's name in config.json to its model.
 
-An entry couples the name (`architectures[0]`) with the typed configuration
+An entry couples the name (`architectures[0]`, or `architecture`) with the typed configuration
 class and the function that composes the model from parts.  lucciola has no
 registry: its engine holds a QwenModel by value (include/async_engine.h:40).
 """
@@ -38,8 +38,11 @@ def resolve_architecture(config_dict: Mapping[str, Any]) -> Architecture:
     """The registered architecture that config.json names."""
     _ensure_builtin()
     archs = config_dict.get("architectures")
+    if isinstance(config_dict.get("architecture"), str) and not archs:
+        archs = [config_dict["architecture"]]          # some designs name themselves with one string
     if not archs or not isinstance(archs, (list, tuple)):
-        raise ConfigError("config.json has no 'architectures' list; known architectures: " + ", ".join(sorted(_REGISTRY)))
+        raise ConfigError("config.json names no architecture ('architectures' list or 'architecture'); known architectures: "
+                          + ", ".join(sorted(_REGISTRY)))
     name = archs[0]
     if name not in _REGISTRY:
         raise ConfigError(f"unknown architecture {name!r}; known architectures: " + ", ".join(sorted(_REGISTRY)))
@@ -47,5 +50,5 @@ def resolve_architecture(config_dict: Mapping[str, Any]) -> Architecture:
 
 
 def _ensure_builtin() -> None:
-    # The built-in model registers itself on import.
-    from ..models import qwen3  # noqa: F401
+    # The built-in models register themselves on import.
+    from ..models import qwen3, riruzen  # noqa: F401

@@ -8,6 +8,11 @@
 // the 32-bit path (no reduced-precision matrix mode: FFMA only) and the
 // fallback for shapes the tensor-core kernel refuses.  X, W and Y may each be
 // 32-bit or bfloat16.
+//
+// lb_gemm_plain_batched runs the same kernel over gridDim.z independent products (one per head of a
+// mixer whose heads each have a matrix of their own): batch b reads x + b * bx, w + b * bw and writes
+// y + b * by.  An optional gate (32-bit, [M, batches * N] with row stride ldg) multiplies element
+// (m, n) of batch b by sigmoid(gate[m, b * N + n]) before the single rounding.
 #include "common.cuh"
 
 namespace lb {
@@ -17,13 +22,16 @@ constexpr int PG_BM = 64, PG_BN = 64, PG_BK = 16;
 template <typename TX, typename TW, typename TY>
 __global__ void __launch_bounds__(256)
 gemm_plain_kernel(TY* __restrict__ y, const TX* __restrict__ x, const TW* __restrict__ w, int M, int N,
-                  int K, long long ldx, long long ldy) {
+                  int K, long long ldx, long long ldy, long long bx, long long bw, long long by,
+                  const float* __restrict__ gate, long long ldg) {
   __shared__ float xs[PG_BK][PG_BM + 4];
   __shared__ float ws[PG_BK][PG_BN + 4];
   pdl_trigger();
   pdl_wait();
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * PG_BM, n0 = blockIdx.x * PG_BN;
+  x += (size_t)blockIdx.z * bx; w += (size_t)blockIdx.z * bw; y += (size_t)blockIdx.z * by;
+  if (gate) gate += (size_t)blockIdx.z * N;
   const int tr = tid / 16, tc = tid % 16;  // thread owns rows tr*4.., cols tc*4..
   float acc[4][4];
 #pragma unroll
@@ -62,16 +70,21 @@ gemm_plain_kernel(TY* __restrict__ y, const TX* __restrict__ x, const TW* __rest
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int gn = n0 + tc * 4 + j;
-      if (gn < N) y[(size_t)gm * ldy + gn] = from_f32<TY>(acc[i][j]);
+      if (gn >= N) continue;
+      float v = acc[i][j];
+      if (gate) v *= 1.f / (1.f + expf(-gate[(size_t)gm * ldg + gn]));
+      y[(size_t)gm * ldy + gn] = from_f32<TY>(v);
     }
   }
 }
 
 template <typename TX, typename TW, typename TY>
 void launch_gemm_plain(void* y, const void* x, const void* w, int M, int N, int K, long long ldx,
-                       long long ldy, cudaStream_t stream) {
-  dim3 grid((N + PG_BN - 1) / PG_BN, (M + PG_BM - 1) / PG_BM);
-  launch(gemm_plain_kernel<TX, TW, TY>, grid, dim3(256), 0, stream, (TY*)y, (const TX*)x, (const TW*)w, M, N, K, ldx, ldy);
+                       long long ldy, cudaStream_t stream, int batches = 1, long long bx = 0, long long bw = 0,
+                       long long by = 0, const float* gate = nullptr, long long ldg = 0) {
+  dim3 grid((N + PG_BN - 1) / PG_BN, (M + PG_BM - 1) / PG_BM, batches);
+  launch(gemm_plain_kernel<TX, TW, TY>, grid, dim3(256), 0, stream, (TY*)y, (const TX*)x, (const TW*)w, M, N, K, ldx, ldy,
+         bx, bw, by, gate, ldg);
 }
 
 }  // namespace lb
@@ -92,5 +105,26 @@ LB_EXPORT int lb_gemm_plain(void* y, int y_dtype, const void* x, int x_dtype, co
     })
   })
   LB_CHECK_LAUNCH("gemm_plain");
+  return 0;
+}
+
+LB_EXPORT int lb_gemm_plain_batched(void* y, int y_dtype, const void* x, int x_dtype, const void* w, int w_dtype,
+                                    int batches, int M, int N, int K, long long ldx, long long ldy, long long bx,
+                                    long long bw, long long by, const float* gate, long long ldg, cudaStream_t stream) {
+  LB_CHECK_ARG(lb::valid_dtype(y_dtype) && lb::valid_dtype(x_dtype) && lb::valid_dtype(w_dtype),
+               "gemm_plain_batched: bad dtype");
+  LB_CHECK_ARG(M >= 0 && N > 0 && K > 0 && batches > 0 && batches <= 65535 && ldx >= K && ldy >= N,
+               "gemm_plain_batched: bad sizes batches=%d M=%d N=%d K=%d", batches, M, N, K);
+  LB_CHECK_ARG(gate == nullptr || ldg >= (long long)batches * N, "gemm_plain_batched: the gate's rows are shorter than batches * N");
+  LB_CHECK_ARG((M + lb::PG_BM - 1) / lb::PG_BM <= 65535, "gemm_plain_batched: too many rows (%d)", M);
+  if (M == 0) return 0;
+  LB_DISPATCH_DTYPE(x_dtype, TX, {
+    LB_DISPATCH_DTYPE(w_dtype, TW, {
+      LB_DISPATCH_DTYPE(y_dtype, TY, {
+        lb::launch_gemm_plain<TX, TW, TY>(y, x, w, M, N, K, ldx, ldy, stream, batches, bx, bw, by, gate, ldg);
+      })
+    })
+  })
+  LB_CHECK_LAUNCH("gemm_plain_batched");
   return 0;
 }

@@ -265,14 +265,17 @@ struct GemmParams {
   int out_dtype;        // LB_F32 or LB_BF16
   int cluster;          // > 0: the splits of a tile form a thread-block cluster of this size and add
                         // their partials through distributed shared memory (no workspace, no counters)
-  int swiglu;           // 1: the weight rows alternate in blocks of 64 between "gate" and "up" rows of the same 64
-                        // features; the output has N/2 columns and holds silu(gate) * up (computed in 32-bit)
+  int swiglu;           // 1, 2: the weight rows alternate in blocks of 64 between "gate" and "up" rows of the same 64
+                        // features; the output has N/2 columns and holds act(gate) * up (computed in 32-bit) with
+                        // act = silu (1) or relu (2)
   unsigned long long wait_cycles = WAIT_CYCLES;   // after this many clock cycles a wait on a barrier gives up
   int skip_loads = 0;   // tests of the give-up path only: the producer requests nothing, so the first wait runs out
 };
 
 // silu(g) * u; the quotient by the fast division (2 ulp), the result is rounded to bfloat16 or summed with like terms afterwards
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
+// act(g) * u for the activation a gated feed-forward names: 1 silu, 2 relu
+__device__ __forceinline__ float gated_mul(int act, float g, float u) { return act == 2 ? fmaxf(g, 0.f) * u : silu_mul(g, u); }
 
 template <int BT>
 __host__ __device__ constexpr int tmem_cols() { return BT < 32 ? 32 : BT; }
@@ -473,7 +476,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (feature < (p.N >> 1)) {
           for (int j = t >> 6; j < BT && m0 + j < p.M; j += 2) {
             const float rf = p.rs.on ? row_f[j] : 1.f;
-            const float v = silu_mul(part_smem[j * BM + f] * rf, part_smem[j * BM + f + 64] * rf);
+            const float v = gated_mul(p.swiglu, part_smem[j * BM + f] * rf, part_smem[j * BM + f + 64] * rf);
             if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)(m0 + j) * p.ldy + feature] = v;
             else ((bf16*)p.y)[(size_t)(m0 + j) * p.ldy + feature] = __float2bfloat16_rn(v);
           }
@@ -542,7 +545,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const uint32_t a = smem_base + (uint32_t)j * (BM * 4u) + (uint32_t)f * 4u;
             const float rf = p.rs.on ? row_factor(p.rs, m) : 1.f;
             const float g = cluster_sum_f32(a, splits) * rf, u = cluster_sum_f32(a + 256u, splits) * rf;
-            const float v = silu_mul(g, u);
+            const float v = gated_mul(p.swiglu, g, u);
             if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)m * p.ldy + feature] = v;
             else ((bf16*)p.y)[(size_t)m * p.ldy + feature] = __float2bfloat16_rn(v);
           }
@@ -1064,7 +1067,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
           if (m < p.M && feature < (p.N >> 1)) {
             float v[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = silu_mul(__uint_as_float(g[j]) * rf, __uint_as_float(u[j]) * rf);
+            for (int j = 0; j < 16; ++j) v[j] = gated_mul(p.swiglu, __uint_as_float(g[j]) * rf, __uint_as_float(u[j]) * rf);
             if (vec_store && feature + 16 <= (p.N >> 1)) {
               if (p.out_dtype == LB_F32) {
                 float4* dst = reinterpret_cast<float4*>((float*)p.y + (size_t)m * p.ldy + feature);

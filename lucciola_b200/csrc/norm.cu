@@ -113,7 +113,135 @@ __global__ void add_rmsnorm_row_kernel(TO* __restrict__ out, float* __restrict__
     store4(o + 4 * (q * nt + tid), make_float4(v[q].x * inv * w[q].x, v[q].y * inv * w[q].y, v[q].z * inv * w[q].z, v[q].w * inv * w[q].w));
 }
 
+// RMSNorm in groups: the row is cut into `groups` equal consecutive parts and each part is divided by its own
+// sqrt(mean(part^2) + eps); the whole is multiplied by the weight.  Up to two deltas are added to the residual
+// stream first (in 32-bit, a then b), for blocks whose sublayers run side by side and leave their outputs unsummed.
+// A group is walked by `wpg` warps; the partial sums of a group's warps are added in warp order, so a row's result
+// does not depend on the batch.  The row is read from global memory for the sums and again (from cache) for the output.
+template <typename TD, typename TO>
+__global__ void add_group_rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ residual, const TD* __restrict__ delta_a,
+                                         const TD* __restrict__ delta_b, const float* __restrict__ weight,
+                                         const int* __restrict__ rows, int hidden, int groups, int wpg, float eps) {
+  __shared__ float part[32];
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x;
+  const int src = rows ? rows[i] : i;
+  float* r = residual + (size_t)src * hidden;
+  const TD* da = delta_a ? delta_a + (size_t)src * hidden : nullptr;
+  const TD* db = delta_b ? delta_b + (size_t)src * hidden : nullptr;
+  TO* o = out + (size_t)i * hidden;
+  const bool update = (rows == nullptr) && (da != nullptr || db != nullptr);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int gsize = hidden / groups;
+  const int per_round = nwarps / wpg;                 // groups worked on at a time
+  const int seg = warp % wpg;
+  for (int g0 = 0; g0 < groups; g0 += per_round) {
+    const int g = g0 + warp / wpg;
+    float ss = 0.f;
+    if (g < groups) {
+      for (int j = seg * 32 + lane; j < gsize; j += wpg * 32) {
+        const int c = g * gsize + j;
+        float v = r[c];
+        if (da) v += to_f32(da[c]);
+        if (db) v += to_f32(db[c]);
+        if (update) r[c] = v;
+        ss += v * v;
+      }
+    }
+    ss = warp_sum(ss);
+    __syncthreads();                                  // `part` may still be read by the groups handled just before
+    if (lane == 0) part[warp] = ss;
+    __syncthreads();
+    if (g < groups) {
+      float tot = 0.f;
+      for (int k = 0; k < wpg; ++k) tot += part[(warp / wpg) * wpg + k];
+      const float inv = 1.f / sqrtf(tot / (float)gsize + eps);
+      for (int j = seg * 32 + lane; j < gsize; j += wpg * 32) {
+        const int c = g * gsize + j;
+        float v = r[c];                               // own earlier write, or the untouched row
+        if (!update) {
+          if (da) v += to_f32(da[c]);
+          if (db) v += to_f32(db[c]);
+        }
+        o[c] = from_f32<TO>(v * inv * weight[c]);
+      }
+    }
+  }
+}
+
 }  // namespace lb
+
+// out = group RMSNorm of (residual [+ delta_a] [+ delta_b]); the sum is written back to the residual stream when
+// rows == nullptr.  hidden must be a multiple of groups.
+LB_EXPORT int lb_add_group_rmsnorm(void* out, int out_dtype, float* residual, const void* delta_a, const void* delta_b,
+                                   int delta_dtype, const float* weight, const int* rows, int num_rows, int hidden,
+                                   int groups, float eps, cudaStream_t stream) {
+  LB_CHECK_ARG(lb::valid_dtype(out_dtype) && lb::valid_dtype(delta_dtype), "add_group_rmsnorm: bad dtype");
+  LB_CHECK_ARG(num_rows >= 0 && hidden > 0 && groups > 0 && hidden % groups == 0,
+               "add_group_rmsnorm: bad sizes rows=%d hidden=%d groups=%d", num_rows, hidden, groups);
+  if (num_rows == 0) return 0;
+  // about 128 elements a warp, 1 to 16 warps; a group gets a whole number of warps, or a warp whole groups in turn
+  int want = (hidden + 127) / 128;
+  if (want > 16) want = 16;
+  if (want < 1) want = 1;
+  int wpg = want / groups;
+  if (wpg < 1) wpg = 1;
+  int per_round = want / wpg;
+  if (per_round > groups) per_round = groups;
+  if (per_round < 1) per_round = 1;
+  const int warps = wpg * per_round;
+  LB_DISPATCH_DTYPE(delta_dtype, TD, {
+    LB_DISPATCH_DTYPE(out_dtype, TO, {
+      lb::launch(lb::add_group_rmsnorm_kernel<TD, TO>, dim3(num_rows), dim3(warps * 32), 0, stream, (TO*)out, residual,
+                 (const TD*)delta_a, (const TD*)delta_b, weight, rows, hidden, groups, wpg, eps);
+    })
+  })
+  LB_CHECK_LAUNCH("add_group_rmsnorm");
+  return 0;
+}
+
+// x *= factor, 32-bit (the scale of a model's logits).
+namespace lb {
+__global__ void scale_kernel(float* __restrict__ x, long long n, float factor) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) x[i] *= factor;
+}
+}  // namespace lb
+
+// residual += delta in 32-bit, for a block that must hand on one delta where it has two.
+namespace lb {
+template <typename TD>
+__global__ void add_into_kernel(float* __restrict__ residual, const TD* __restrict__ delta, long long n) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    residual[i] += to_f32(delta[i]);
+}
+}  // namespace lb
+
+LB_EXPORT int lb_add_into(float* residual, const void* delta, int delta_dtype, long long n, cudaStream_t stream) {
+  LB_CHECK_ARG(residual && delta && n >= 0 && lb::valid_dtype(delta_dtype), "add_into: bad arguments");
+  if (n == 0) return 0;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  LB_DISPATCH_DTYPE(delta_dtype, TD, {
+    lb::launch(lb::add_into_kernel<TD>, dim3((unsigned)blocks), dim3(256), 0, stream, residual, (const TD*)delta, n);
+  })
+  LB_CHECK_LAUNCH("add_into");
+  return 0;
+}
+
+LB_EXPORT int lb_scale(float* x, long long n, float factor, cudaStream_t stream) {
+  LB_CHECK_ARG(x && n >= 0, "scale: bad arguments");
+  if (n == 0) return 0;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  lb::launch(lb::scale_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, n, factor);
+  LB_CHECK_LAUNCH("scale");
+  return 0;
+}
 
 LB_EXPORT int lb_add_rmsnorm(void* out, int out_dtype, float* residual, const void* delta,
                              int delta_dtype, const float* weight, const int* rows, int num_rows,

@@ -44,7 +44,7 @@ def main(argv: list[str] | None = None) -> int:
     out = Path(args.out)
     out.mkdir(parents=True, exist_ok=True)
     pages = -(-args.max_tokens // args.block_size)
-    options = EngineOptions(dtype=args.dtype, block_size=args.block_size, max_blocks=pages, max_num_seqs=8,
+    options = EngineOptions(dtype=args.dtype, block_size=args.block_size, max_blocks=pages, max_num_seqs=4,
                             use_cuda_graph=args.cuda_graph, graph_after=1, max_shape_graphs=256)
     runner = build_runner(args.model, options, num_pages=pages)
 

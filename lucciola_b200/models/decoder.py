@@ -46,7 +46,7 @@ class DecoderModel(Part):
             elif c.cache not in written:
                 raise ValueError(f"call {i} reads cache {c.cache} before any call has written it")
             else:
-                a, b = self.blocks[self.calls[written[c.cache]].block].mixer.cache_request(), self.blocks[c.block].mixer.cache_request()
+                a, b = self.blocks[self.calls[written[c.cache]].block].cache_request(), self.blocks[c.block].cache_request()
                 if a != b:
                     raise ValueError(f"call {i} reads cache {c.cache} but its mixer wants {b}, the cache holds {a}")
         if sorted(written) != list(range(len(written))):
@@ -60,22 +60,27 @@ class DecoderModel(Part):
     def ignored_names(self) -> list[str]:
         return self.head.ignored_names()
 
-    def cache_requests(self) -> list[KVPages | StateSlot | None]:
-        """What each cache id has to hold, as asked by the mixer that writes it."""
-        return [self.blocks[self.calls[self._writer[j]].block].mixer.cache_request() for j in range(self.num_caches)]
+    def cache_requests(self) -> list[KVPages | StateSlot | None | tuple]:
+        """What each cache id has to hold, as asked by the block that writes it (its mixer's needs, and the block's own)."""
+        return [self.blocks[self.calls[self._writer[j]].block].cache_request() for j in range(self.num_caches)]
 
     def forward(self, token_ids: torch.Tensor, step: StepContext, caches: Sequence[object],
                 logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Run the tokens of one step; float32 logits [R, vocab] for the rows asked for (None if none)."""
-        residual = self.embedding.forward(token_ids)
+        residual = self.embedding.forward(token_ids, step.positions) if getattr(self.embedding, "uses_positions", False) else self.embedding.forward(token_ids)
         delta = None
         for i, c in enumerate(self.calls):
             # what the call after this one offers to take over from this one's last product (see Block.entry_sink)
             nxt = self.calls[i + 1] if i + 1 < len(self.calls) else None
             block = self.blocks[c.block]
             next_sink = self.blocks[nxt.block].entry_sink(residual, step.num_tokens, nxt.write_cache) if nxt is not None else None
+            # a block whose sublayers run side by side may leave their outputs unsummed when the norm that adds them
+            # to the residual stream takes both (see Block.offers_delta_parts)
+            parts_ok = (self.blocks[nxt.block].takes_delta_parts if nxt is not None else self.final_norm.takes_delta_parts)
             if next_sink is not None and block.accepts_next_sink:
                 residual, delta = block.forward(residual, delta, step, caches[c.cache], c.write_cache, next_sink=next_sink)
+            elif block.offers_delta_parts and parts_ok:
+                residual, delta = block.forward(residual, delta, step, caches[c.cache], c.write_cache, delta_parts=True)
             else:
                 residual, delta = block.forward(residual, delta, step, caches[c.cache], c.write_cache)
         if logit_rows is None or logit_rows.shape[0] == 0:

@@ -30,14 +30,26 @@ def dtype_code(dt: torch.dtype) -> int:
 
 
 _SIGNATURES = {
-    "lb_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "lb_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+    "lb_add_group_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                             c_float, c_void_p],
+    "lb_scale": [c_void_p, c_longlong, c_float, c_void_p],
+    "lb_add_into": [c_void_p, c_void_p, c_int, c_longlong, c_void_p],
+    "lb_causal_taps": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "lb_causal_taps_state": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "lb_latent_norm": [c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                       c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+    "lb_gated_recurrence": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "lb_gemm_plain_batched": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong,
+                              c_longlong, c_longlong, c_longlong, c_longlong, c_void_p, c_longlong, c_void_p],
     "lb_add_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
     "lb_rope_kv": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p,
                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "lb_attention_plain": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                            c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
-    "lb_swiglu": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p],
+    "lb_swiglu": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p],
     "lb_gemm_plain": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_longlong,
                       c_longlong, c_void_p],
     "lb_gemm_tcgen05": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p,
@@ -103,12 +115,110 @@ def current_stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def embedding(out: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, stream: int) -> None:
-    """out[t, :] = table[ids[t], :] as float32."""
+def embedding(out: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, stream: int,
+              pos_table: torch.Tensor | None = None, positions: torch.Tensor | None = None) -> None:
+    """out[t, :] = table[ids[t], :] as float32; with a table of position vectors, + pos_table[positions[t], :]."""
     _check(out, "embedding output", torch.float32); _check(ids, "token ids", torch.int32); _check(table, "embedding table")
     T, H = out.shape
+    if pos_table is not None:
+        _check(pos_table, "position table", table.dtype); _check(positions, "positions", torch.int32)
+        if pos_table.shape[1] != H:
+            raise KernelError(f"position vectors have {pos_table.shape[1]} values, the embedding {H}")
     _call("lb_embedding", out.data_ptr(), ids.data_ptr(), table.data_ptr(), dtype_code(table.dtype), T, H,
-          table.shape[0], stream)
+          table.shape[0], _ptr(pos_table), _ptr(positions), pos_table.shape[0] if pos_table is not None else 0, stream)
+
+
+def add_group_rmsnorm(out: torch.Tensor, residual: torch.Tensor, deltas: tuple, weight: torch.Tensor, groups: int,
+                      eps: float, stream: int, rows: torch.Tensor | None = None) -> None:
+    """residual += sum of up to two deltas (when rows is None); out = the row's `groups` equal consecutive parts each
+    divided by its own sqrt(mean(part^2) + eps), times weight; on `rows` if given."""
+    _check(out, "norm output"); _check(residual, "residual", torch.float32); _check(weight, "norm weight", torch.float32)
+    deltas = tuple(d for d in deltas if d is not None)
+    if len(deltas) > 2:
+        raise KernelError("the group norm adds at most two deltas")
+    for d in deltas:
+        _check(d, "delta", deltas[0].dtype)
+        if d.shape != residual.shape:
+            raise KernelError("a delta must have the residual's shape")
+    if rows is not None:
+        _check(rows, "row index", torch.int32)
+    H = out.shape[-1]
+    _call("lb_add_group_rmsnorm", out.data_ptr(), dtype_code(out.dtype), residual.data_ptr(),
+          _ptr(deltas[0]) if deltas else None, _ptr(deltas[1]) if len(deltas) > 1 else None,
+          dtype_code(deltas[0].dtype) if deltas else F32, weight.data_ptr(), _ptr(rows), out.shape[0], H, groups, eps, stream)
+
+
+def add_into(residual: torch.Tensor, delta: torch.Tensor, stream: int) -> None:
+    """residual += delta, in place, the sum in float32."""
+    _check(residual, "residual", torch.float32); _check(delta, "delta")
+    if residual.shape != delta.shape:
+        raise KernelError("residual and delta must have one shape")
+    _call("lb_add_into", residual.data_ptr(), delta.data_ptr(), dtype_code(delta.dtype), residual.numel(), stream)
+
+
+def scale_(x: torch.Tensor, factor: float, stream: int) -> None:
+    """x *= factor, in place, float32."""
+    _check(x, "tensor to scale", torch.float32)
+    _call("lb_scale", x.data_ptr(), x.numel(), factor, stream)
+
+
+def causal_taps(out: torch.Tensor, h: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | None, step, stream: int) -> None:
+    """out_t = h_t + sum_j weight[:, j] * h_(t - taps + 1 + j) over each sequence's tokens in order; what lies before
+    a portion is read from state[slot] ([taps - 1, width], oldest first).  The state is not changed."""
+    _check(out, "convolution output", h.dtype); _check(h, "convolution input"); _check(weight, "taps", torch.float32)
+    T, W = h.shape
+    taps = weight.shape[1]
+    if state is not None:
+        _check(state, "convolution state", h.dtype)
+    _call("lb_causal_taps", dtype_code(h.dtype), out.data_ptr(), h.data_ptr(), weight.data_ptr(), _ptr(state),
+          step.token_seq.data_ptr(), step.cu_tokens.data_ptr(), step.state_slots.data_ptr(), T, W, taps, stream)
+
+
+def causal_taps_state(state: torch.Tensor, h: torch.Tensor, taps: int, step, stream: int) -> None:
+    """state[slot] = the last taps - 1 rows of (state[slot] ++ this step's rows of the sequence)."""
+    _check(state, "convolution state", h.dtype); _check(h, "convolution input")
+    _call("lb_causal_taps_state", dtype_code(h.dtype), state.data_ptr(), h.data_ptr(), step.cu_tokens.data_ptr(),
+          step.state_slots.data_ptr(), step.num_seqs, h.shape[1], taps, stream)
+
+
+def latent_norm(pre: torch.Tensor, q_col: int, kv_col: int, q_rank: int, kv_rank: int, q_w: torch.Tensor, kv_w: torch.Tensor,
+                q_out: torch.Tensor, pages: torch.Tensor, step, block_table: torch.Tensor, page_size: int, eps: float,
+                stream: int) -> None:
+    """RMSNorm of the two latents in the float32 rows of `pre`: the query latent goes to q_out [T, q_rank], the
+    key/value latent to the token's place in `pages` ([pages, 1, page_size, kv_rank])."""
+    _check(pre, "down-projections", torch.float32); _check(q_w, "query latent norm", torch.float32)
+    _check(kv_w, "latent norm", torch.float32); _check(q_out, "query latent"); _check(pages, "latent pages", q_out.dtype)
+    _check(block_table, "block table", torch.int32)
+    _call("lb_latent_norm", dtype_code(q_out.dtype), pre.data_ptr(), pre.stride(0), q_col, kv_col, q_rank, kv_rank,
+          q_w.data_ptr(), kv_w.data_ptr(), q_out.data_ptr(), pages.data_ptr(), step.positions.data_ptr(),
+          step.token_seq.data_ptr(), block_table.data_ptr(), pre.shape[0], page_size, block_table.shape[1], eps, stream)
+
+
+def gated_recurrence(pre: torch.Tensor, q_col: int, f_col: int, v_col: int, bias: torch.Tensor, lower: torch.Tensor,
+                     state: torch.Tensor, out: torch.Tensor, step, heads: int, dim: int, vdim: int, stream: int) -> None:
+    """The HGRN2 recurrence over this step's tokens: per head S <- diag(f) S + (1 - f) v^T, out = S^T q with
+    q = silu(pre[:, q_col..]), f = lower + (1 - lower) sigmoid(pre[:, f_col..] + bias), v = pre[:, v_col..];
+    state [slots + 1, heads, dim, vdim] float32 is read and written at each sequence's slot; out [T, heads * vdim] float32."""
+    _check(pre, "input projections", torch.float32); _check(bias, "gate bias", torch.float32)
+    _check(lower, "lower bound", torch.float32); _check(state, "recurrent state", torch.float32)
+    _check(out, "recurrence output", torch.float32)
+    _call("lb_gated_recurrence", pre.data_ptr(), pre.stride(0), q_col, f_col, v_col, bias.data_ptr(), lower.data_ptr(),
+          state.data_ptr(), out.data_ptr(), step.cu_tokens.data_ptr(), step.state_slots.data_ptr(), step.num_seqs,
+          heads, dim, vdim, stream)
+
+
+def gemm_heads(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int, gate: torch.Tensor | None = None) -> None:
+    """y[t, h, :] = x[t, h, :] . w[h]^T for w [heads, N, K], one product a head, 32-bit sums on the ordinary pipes.
+    With `gate` (float32 [T, >= heads * N], row-strided): y[t, h, n] *= sigmoid(gate[t, h * N + n]) before the rounding."""
+    T, H, K = x.shape
+    N = w.shape[1]
+    _check(x, "x"); _check(w, "per-head weights"); _check(y, "y")
+    if tuple(w.shape) != (H, N, K) or tuple(y.shape) != (T, H, N):
+        raise KernelError(f"per-head product shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
+    if gate is not None and (gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape[0] != T or gate.shape[1] != H * N):
+        raise KernelError("the gate must be float32 [T, heads * N] with unit column stride")
+    _call("lb_gemm_plain_batched", y.data_ptr(), dtype_code(y.dtype), x.data_ptr(), dtype_code(x.dtype), w.data_ptr(),
+          dtype_code(w.dtype), H, T, N, K, H * K, H * N, K, N * K, N, _ptr(gate), gate.stride(0) if gate is not None else 0, stream)
 
 
 def add_rmsnorm(out: torch.Tensor, residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor,
@@ -165,13 +275,17 @@ def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
           head_dim, page_size, block_table.shape[1], window, scale, stream)
 
 
-def swiglu(out: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, stream: int) -> None:
-    """out = silu(gate) * up; gate and up are 2-d views with the same row stride."""
+GATE_ACTS = {"silu": 0, "relu": 1}
+
+
+def swiglu(out: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, stream: int, act: str = "silu") -> None:
+    """out = act(gate) * up with act silu or relu; gate and up are 2-d views with the same row stride."""
     if gate.stride(0) != up.stride(0) or gate.stride(1) != 1 or up.stride(1) != 1:
         raise KernelError("gate and up need the same row stride and unit column stride")
     _check(out, "swiglu output", gate.dtype)
     T, inter = out.shape
-    _call("lb_swiglu", dtype_code(out.dtype), out.data_ptr(), gate.data_ptr(), up.data_ptr(), gate.stride(0), T, inter, stream)
+    _call("lb_swiglu", dtype_code(out.dtype), out.data_ptr(), gate.data_ptr(), up.data_ptr(), gate.stride(0), T, inter,
+          GATE_ACTS[act], stream)
 
 
 def gemm_plain(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int) -> None:
@@ -235,11 +349,13 @@ def _row_scale(sumsq: torch.Tensor | None, width: int, eps: float):
 
 
 def gemm_tcgen05(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int, force_bt: int = 0,
-                 force_splits: int = 0, swiglu: bool = False, sumsq: torch.Tensor | None = None, eps: float = 0.0) -> None:
+                 force_splits: int = 0, swiglu: bool = False, sumsq: torch.Tensor | None = None, eps: float = 0.0,
+                 act: str = "silu") -> None:
     """y[M, N] = x[M, K] . w[N, K]^T on the tensor cores (tcgen05, accumulators in tensor memory).
 
     With `swiglu` the rows of w alternate in blocks of 64 between gate rows and up rows of the same 64
-    features (see interleave_gate_up), and y[M, N/2] = silu(x . gate^T) * (x . up^T), formed in the epilogue.
+    features (see interleave_gate_up), and y[M, N/2] = act(x . gate^T) * (x . up^T), formed in the epilogue
+    (act: "silu" or "relu").
     With `sumsq` [M, tiles] the rows of x lack the factor of an RMSNorm over K values: row m of the product is
     multiplied by rsqrt(sum(sumsq[m]) / K + eps), before the activation if there is one (see gemm_tcgen05_addnorm)."""
     M, K = x.shape
@@ -251,7 +367,7 @@ def gemm_tcgen05(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int,
     ws, counters = _gemm_scratch(x.device)
     _call("lb_gemm_tcgen05", y.data_ptr(), dtype_code(y.dtype), x.data_ptr(), w.data_ptr(), M, N, K,
           x.stride(0) if M > 1 else K, y.stride(0) if M > 1 else y.shape[1], ws.data_ptr(), ws.numel(), counters.data_ptr(),
-          counters.numel(), force_bt, force_splits, 1 if swiglu else 0, _row_scale(sumsq, K, eps), stream)
+          counters.numel(), force_bt, force_splits, (1 + GATE_ACTS[act]) if swiglu else 0, _row_scale(sumsq, K, eps), stream)
 
 
 class LbHeadEpilogue(ctypes.Structure):

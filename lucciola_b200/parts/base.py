@@ -15,11 +15,13 @@ Norm              forward(x, out_dtype)            -> normed copy
                   add_forward(residual, delta, out_dtype, rows=None)
                                                    residual += delta; -> norm(residual) [on rows]
 PositionEncoding  rotary_table() / apply(q, k, positions)
-Mixer             cache_request() -> KVPages | StateSlot | None
+Mixer             cache_request() -> KVPages | StateSlot | None | a tuple of these (the cache then arrives as a
+                                                   tuple of views in the same order)
                   forward(h, step, cache) -> [T, hidden] in the activation type
                   plan_key(), plan(batch) -> StepPlan   optional: work lists its kernels read on the device
 FeedForward       forward(h, step) -> [T, hidden]
 Block             mixer, forward(residual, delta, step, cache) -> (residual, delta)
+                  cache_request()                  the mixer's, unless the block keeps state of its own beside it
 
 `step` is the StepContext: what a part may know about the batch.
 """
@@ -36,7 +38,7 @@ import torch
 class ParamSpec:
     name: str                       # full tensor name in the checkpoint
     shape: tuple[int, ...]
-    init: str = "linear"            # "linear" | "embedding" | "norm": how random weights are drawn
+    init: str = "linear"            # "linear" | "embedding" | "norm" | "unit": how random weights are drawn
     integer: bool = False           # integer tables are kept as int32
 
 
@@ -46,6 +48,7 @@ class KVPages:
     num_kv_heads: int
     head_dim: int
     window: int = 0                 # 0: all keys; W: the last W keys (the query's own included)
+    shared: bool = False            # True: one vector a token serves as key and as value (a latent); half the memory
 
 
 @dataclass(frozen=True)
@@ -70,7 +73,8 @@ class Runtime:
 
 @dataclass
 class KVCacheView:
-    """One cache layer of paged keys and values, as a mixer sees it."""
+    """One cache layer of paged keys and values, as a mixer sees it.  For KVPages(shared=True) k and v are the
+    same memory."""
     k: torch.Tensor                 # [pages, kv_heads, page_size, head_dim]
     v: torch.Tensor
     group: int                      # index into StepContext.block_tables
@@ -209,6 +213,10 @@ class Norm(Part):
         add_forward(residual, its output); None for every other kind of norm."""
         return None
 
+    # True: add_forward() also takes a tuple of two tensors as `delta` and adds both (blocks whose sublayers run side
+    # by side hand their outputs on unsummed).
+    takes_delta_parts = False
+
     def add_forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out_dtype: torch.dtype,
                     rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
@@ -225,7 +233,8 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    def cache_request(self) -> KVPages | StateSlot | None:
+    def cache_request(self) -> KVPages | StateSlot | None | tuple:
+        """What this mixer keeps of past tokens; a tuple when it keeps several things."""
         return None
 
     def plan_key(self) -> Optional[Hashable]:
@@ -262,6 +271,15 @@ class FeedForward(Part):
 class Block(Part):
     mixer: Mixer
     accepts_next_sink = False       # True: forward() takes the keyword `next_sink`
+    # True: forward() takes the keyword `delta_parts`; with it the block may return a tuple of two tensors as its delta
+    # (the outputs of sublayers that run side by side), for a norm that adds both (Norm.takes_delta_parts).
+    offers_delta_parts = False
+    takes_delta_parts = False       # True: forward() takes such a tuple as `delta` (its first norm adds both)
+
+    def cache_request(self) -> KVPages | StateSlot | None | tuple:
+        """What a call of this block keeps of past tokens: the mixer's cache, unless the block has state of its own
+        beside it (then a tuple, and forward() gets a tuple of views in the same order)."""
+        return self.mixer.cache_request()
 
     def entry_sink(self, residual: torch.Tensor, num_tokens: int, write_cache: bool) -> Optional[NormSink]:
         """Not None: the block before this one may hand its output over already added to the residual stream and
@@ -270,7 +288,8 @@ class Block(Part):
 
     def forward(self, residual: torch.Tensor, delta, step: StepContext, cache, write_cache: bool = True,
                 next_sink: Optional[NormSink] = None) -> tuple[torch.Tensor, object]:
-        """`delta`: what the block before left to be added (a tensor, or None for the first block), or RowScaled when
-        it went through this block's entry_sink.  Returns the residual stream and this block's own delta, RowScaled
+        """`delta`: what the block before left to be added (a tensor, a tuple of tensors whose sum is meant when the
+        block before says `delta_parts` and this block's first norm takes them, or None for the first block), or
+        RowScaled when it went through this block's entry_sink.  Returns the residual stream and this block's own delta, RowScaled
         if it used `next_sink`."""
         raise NotImplementedError

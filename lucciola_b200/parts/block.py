@@ -9,7 +9,9 @@ from typing import Optional
 
 import torch
 
+from .. import ops
 from .base import Block, FeedForward, Mixer, Norm, NormSink, Part, RowScaled, StepContext
+from .causal_taps import CausalTaps
 
 
 class PreNormBlock(Block):
@@ -48,3 +50,48 @@ class PreNormBlock(Block):
         if next_sink is not None and self.feed_forward.accepts_sink:
             return residual, self.feed_forward.forward(h, step, sink=next_sink)
         return residual, self.feed_forward.forward(h, step)
+
+
+class ParallelBlock(Block):
+    """One norm, two sublayers side by side: h = norm(r); r += mixer(u) + ffn(h), where the mixer reads
+    u = input_taps(h) (a short causal convolution over time added to h) if the block has one, else h.  The
+    feed-forward always reads h; a block may have none.
+
+    The block hands its two outputs on unsummed when the norm that follows takes them (`delta_parts`): that norm adds
+    both to the 32-bit residual stream in the pass in which it reads it.  The taps' state (the last inputs of each
+    sequence) lives beside the mixer's cache: the block asks for (taps' state, mixer's cache)."""
+    recordable = True
+    offers_delta_parts = True
+
+    def __init__(self, mixer: Mixer, feed_forward: Optional[FeedForward], norm: Norm, act_dtype: torch.dtype,
+                 input_taps: Optional[CausalTaps] = None):
+        self.mixer, self.feed_forward, self.norm, self.input_taps = mixer, feed_forward, norm, input_taps
+        self.act_dtype = act_dtype
+        self._taps_state = input_taps.cache_request() if input_taps is not None else None
+        self._rt = norm.rt
+
+    @property
+    def takes_delta_parts(self) -> bool:
+        return self.norm.takes_delta_parts
+
+    def children(self) -> list[Part]:
+        return [p for p in (self.norm, self.input_taps, self.mixer, self.feed_forward) if p is not None]
+
+    def cache_request(self):
+        mixer = self.mixer.cache_request()
+        return (self._taps_state, mixer) if self._taps_state is not None else mixer
+
+    def forward(self, residual: torch.Tensor, delta, step: StepContext, cache, write_cache: bool = True,
+                delta_parts: bool = False):
+        h = self.norm.add_forward(residual, delta, self.act_dtype)
+        taps_cache, mixer_cache = cache if self._taps_state is not None else (None, cache)
+        u = self.input_taps.forward(h, step, taps_cache) if self.input_taps is not None else h
+        a = self.mixer.forward(u, step, mixer_cache, write_cache)
+        if self.feed_forward is None:
+            return residual, a
+        b = self.feed_forward.forward(h, step)
+        if delta_parts:
+            return residual, (a, b)
+        # the norm that follows adds one delta only: the mixer's output goes into the residual stream here
+        ops.add_into(residual, a, self._rt.stream)
+        return residual, b

@@ -1,0 +1,96 @@
+"""Latent attention without positions: keys and values of all heads are linear maps of ONE normed latent
+vector per token, and only that latent is kept.
+
+    c_q = rmsnorm(W_dq u) * w_q         q_h = W_uq[h] c_q                       (heads x dim)
+    c   = rmsnorm(W_dkv u) * w_kv       k_h = W_uk[h] c,  v_h = W_uv[h] c        (dim, vdim a head)
+    o_h = softmax_j<=i( q_h . k_h,j * scale ) v_h,j ;  out = W_o ( concat_h o_h * sigmoid(W_g u) )
+
+Because k and v are linear in c, the head's key map moves to the query and its value map behind the sum:
+q_h . (W_uk[h] c_j) = (W_uk[h]^T q_h) . c_j and sum_j p_j W_uv[h] c_j = W_uv[h] (sum_j p_j c_j).  So the
+attention itself runs as `heads` query heads of size kv_rank over one shared "head" whose keys and values
+are both the cached latents, through the same paged attention kernels as grouped-query attention
+(KVPages(1, kv_rank, shared=True): one vector a token, half the memory of separate keys and values), for
+prompts and for decoding alike.  The three maps that read u (W_dq | W_dkv | W_g) are one product with
+32-bit output; the two norms and the write into the pages are one kernel; the per-head maps are one
+batched product each, the second with the sigmoid gate in its epilogue.
+"""
+from __future__ import annotations
+
+from typing import Callable, Hashable, Optional
+
+import torch
+
+from .. import ops
+from .attention import TILE_ROWS, GQAttention, plan_tiles
+from .base import BatchShape, KVCacheView, KVPages, Mixer, ParamSpec, Part, Runtime, StepContext, StepPlan
+from .linear import Linear
+
+
+class LatentAttention(Mixer):
+    recordable = True
+
+    def __init__(self, rt: Runtime, prefix: str, width: int, heads: int, dim: int, vdim: int, q_rank: int, kv_rank: int,
+                 scale: float, eps: float):
+        self.rt, self.prefix = rt, prefix
+        self.width, self.heads, self.dim, self.vdim = width, heads, dim, vdim
+        self.q_rank, self.kv_rank, self.scale, self.eps = q_rank, kv_rank, float(scale), float(eps)
+        # one product for everything that reads the mixer's input: query latent | key/value latent | gate
+        self.down = Linear(rt, [f"{prefix}.dq", f"{prefix}.dkv", f"{prefix}.g"], width, [q_rank, kv_rank, heads * vdim])
+        self.uq = Linear(rt, f"{prefix}.uq", q_rank, heads * dim)
+        self.o = Linear(rt, f"{prefix}.o", heads * vdim, width)
+        self.q_norm_w: torch.Tensor | None = None
+        self.kv_norm_w: torch.Tensor | None = None
+        self.uk_t: torch.Tensor | None = None       # [heads, kv_rank, dim]: W_uk[h]^T, the key map moved to the query
+        self.uv: torch.Tensor | None = None         # [heads, vdim, kv_rank]
+
+    def children(self) -> list[Part]:
+        return [self.down, self.uq, self.o]
+
+    def param_specs(self) -> list[ParamSpec]:
+        p = self.prefix
+        return [ParamSpec(f"{p}.dq.norm", (self.q_rank,), "norm"), ParamSpec(f"{p}.dkv.norm", (self.kv_rank,), "norm"),
+                ParamSpec(f"{p}.uk", (self.heads * self.dim, self.kv_rank)), ParamSpec(f"{p}.uv", (self.heads * self.vdim, self.kv_rank))]
+
+    def bind(self, get: Callable[[str], torch.Tensor]) -> None:
+        p = self.prefix
+        self.q_norm_w = get(f"{p}.dq.norm").to(torch.float32).contiguous()
+        self.kv_norm_w = get(f"{p}.dkv.norm").to(torch.float32).contiguous()
+        self.uk_t = get(f"{p}.uk").view(self.heads, self.dim, self.kv_rank).transpose(1, 2).contiguous()
+        self.uv = get(f"{p}.uv").view(self.heads, self.vdim, self.kv_rank).contiguous()
+
+    def cache_request(self) -> KVPages:
+        return KVPages(1, self.kv_rank, 0, shared=True)
+
+    # The tile lists of the tensor-core attention kernels, as grouped-query attention makes them for a group of
+    # `heads` query heads on one key/value head.
+    def plan_key(self) -> Optional[Hashable]:
+        return ("attention tiles", self.heads) if self.rt.fast_kernels and self.heads <= TILE_ROWS else None
+
+    def plan(self, batch: BatchShape) -> Optional[StepPlan]:
+        if batch.max_q_len == 1:
+            key = (self.heads, len(batch.q_lens))
+            hit = GQAttention._decode_plans.get(key)
+            if hit is None:
+                hit = GQAttention._decode_plans[key] = plan_tiles(batch, self.heads)
+            return hit
+        return plan_tiles(batch, self.heads)
+
+    def forward(self, u: torch.Tensor, step: StepContext, cache: KVCacheView, write_cache: bool = True) -> torch.Tensor:
+        rt = self.rt
+        T, H = u.shape[0], self.heads
+        if not write_cache:
+            raise ops.KernelError("latent attention always writes its own latents")
+        table = step.block_tables[cache.group]
+        pre = self.down.forward(u, out_dtype=torch.float32)                  # [T, q_rank + kv_rank + H * vdim]
+        c_q = rt.empty((T, self.q_rank))
+        ops.latent_norm(pre, 0, self.q_rank, self.q_rank, self.kv_rank, self.q_norm_w, self.kv_norm_w, c_q, cache.k,
+                        step, table, cache.page_size, self.eps, rt.stream)
+        q = self.uq.forward(c_q).view(T, H, self.dim)
+        q_lat = rt.empty((T, H, self.kv_rank))
+        ops.gemm_heads(q_lat, q, self.uk_t, rt.stream)                       # the head's key map, applied to the query
+        mix = rt.empty((T, H, self.kv_rank))
+        ops.attention(q_lat, mix, cache.k, cache.v, step, cache.group, H, 1, self.kv_rank, cache.page_size, 0,
+                      self.scale, rt.stream, plan=step.plans.get(self.plan_key()))
+        gated = rt.empty((T, H, self.vdim))
+        ops.gemm_heads(gated, mix, self.uv, rt.stream, gate=pre[:, self.q_rank + self.kv_rank:])
+        return self.o.forward(gated.view(T, H * self.vdim))

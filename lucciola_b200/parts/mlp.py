@@ -1,7 +1,10 @@
-"""Dense gated feed-forward: down( silu(gate(h)) * up(h) ) (src/qwen.cc:762-794, src/kernels/swiglu.cu:30-36
-of lucciola).  gate and up are one product over the stacked weights; on the bfloat16 path, when the
-intermediate size is a multiple of 64, their rows are interleaved in blocks of 64 and silu(gate) * up is
-formed in that product's epilogue, so the [T, 2 * intermediate] matrix is never written."""
+"""Dense gated feed-forward: down( act(gate(h)) * up(h) ), act = silu (src/qwen.cc:762-794,
+src/kernels/swiglu.cu:30-36 of lucciola) or relu.  gate and up are one product over the stacked weights; on
+the bfloat16 path, when the intermediate size is a multiple of 64, their rows are interleaved in blocks of 64
+and act(gate) * up is formed in that product's epilogue, so the [T, 2 * intermediate] matrix is never written.
+
+GatedFeedForward takes the three tensor names and the activation; SwiGLUFeedForward is the silu one with the
+tensor names of the Qwen3 checkpoints."""
 from __future__ import annotations
 
 from typing import Optional
@@ -13,15 +16,17 @@ from .base import FeedForward, NormSink, Part, RowScaled, Runtime, StepContext
 from .linear import Linear
 
 
-class SwiGLUFeedForward(FeedForward):
+class GatedFeedForward(FeedForward):
     recordable = True
 
-    def __init__(self, rt: Runtime, prefix: str, hidden_size: int, intermediate_size: int):
-        self.rt = rt
+    def __init__(self, rt: Runtime, gate_name: str, up_name: str, down_name: str, hidden_size: int, intermediate_size: int,
+                 act: str = "silu"):
+        if act not in ops.GATE_ACTS:
+            raise ValueError(f"activation {act!r} of a gated feed-forward is not one of {sorted(ops.GATE_ACTS)}")
+        self.rt, self.act = rt, act
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
-        self.gate_up = Linear(rt, [f"{prefix}.gate_proj.weight", f"{prefix}.up_proj.weight"], hidden_size,
-                              [intermediate_size, intermediate_size])
-        self.down = Linear(rt, f"{prefix}.down_proj.weight", intermediate_size, hidden_size)
+        self.gate_up = Linear(rt, [gate_name, up_name], hidden_size, [intermediate_size, intermediate_size])
+        self.down = Linear(rt, down_name, intermediate_size, hidden_size)
         self.fused = False
 
     def children(self) -> list[Part]:
@@ -53,15 +58,21 @@ class SwiGLUFeedForward(FeedForward):
             if not self.row_scaled_ok(h.shape[0]):
                 raise ops.KernelError("this feed-forward was handed rows without their norm factor for a step it cannot take them in")
             act = self.rt.empty((h.shape[0], inter))
-            ops.gemm_tcgen05(act, h.x, self.gate_up.weight, self.rt.stream, swiglu=True, sumsq=h.sumsq, eps=h.eps)
+            ops.gemm_tcgen05(act, h.x, self.gate_up.weight, self.rt.stream, swiglu=True, sumsq=h.sumsq, eps=h.eps, act=self.act)
             return self._down(act, sink)
         if self.fused and ops.gemm_tcgen05_ok(h, h, self.gate_up.weight):
             act = self.rt.empty((h.shape[0], inter))
-            ops.gemm_tcgen05(act, h, self.gate_up.weight, self.rt.stream, swiglu=True)
+            ops.gemm_tcgen05(act, h, self.gate_up.weight, self.rt.stream, swiglu=True, act=self.act)
             return self._down(act, sink)
         if self.fused:
             raise ops.KernelError("the interleaved gate|up weights need the tensor-core product (bfloat16, 16-byte aligned input)")
         gu = self.gate_up.forward(h)
         act = self.rt.empty((h.shape[0], inter))
-        ops.swiglu(act, gu[:, :inter], gu[:, inter:], self.rt.stream)
+        ops.swiglu(act, gu[:, :inter], gu[:, inter:], self.rt.stream, act=self.act)
         return self._down(act, sink)
+
+
+class SwiGLUFeedForward(GatedFeedForward):
+    def __init__(self, rt: Runtime, prefix: str, hidden_size: int, intermediate_size: int):
+        super().__init__(rt, f"{prefix}.gate_proj.weight", f"{prefix}.up_proj.weight", f"{prefix}.down_proj.weight",
+                         hidden_size, intermediate_size, "silu")

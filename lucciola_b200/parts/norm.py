@@ -1,5 +1,8 @@
 """RMSNorm with a weight: y = x * rsqrt(mean(x^2) + eps) * w, statistics and product in 32-bit
-(src/kernels/rmsnorm.cu:57-97 of lucciola; eps is a literal 1e-6 there, a parameter here)."""
+(src/kernels/rmsnorm.cu:57-97 of lucciola; eps is a literal 1e-6 there, a parameter here).
+
+GroupRMSNorm cuts the row into equal consecutive parts with a root mean square each; with one group it is the
+same function (it does not offer itself as a sink of a product's epilogue, which forms one sum a row)."""
 from __future__ import annotations
 
 from typing import Callable, Optional
@@ -35,4 +38,35 @@ class RMSNorm(Norm):
         n = residual.shape[0] if rows is None else rows.shape[0]
         out = self.rt.empty((n, self.size), out_dtype)
         ops.add_rmsnorm(out, residual, delta, self.weight, self.eps, self.rt.stream, rows=rows)
+        return out
+
+
+class GroupRMSNorm(Norm):
+    """y = concat_g( x_g / sqrt(mean(x_g^2) + eps) ) * w over `groups` equal consecutive parts x_g of the row.
+    add_forward() takes one delta or a tuple of two (the outputs of sublayers that run side by side) and adds
+    them to the residual stream in 32-bit."""
+    recordable = True
+    takes_delta_parts = True
+
+    def __init__(self, rt: Runtime, name: str, size: int, groups: int, eps: float):
+        if groups <= 0 or size % groups:
+            raise ValueError(f"a row of {size} cannot be cut into {groups} equal parts")
+        self.rt, self.name, self.size, self.groups, self.eps = rt, name, size, int(groups), float(eps)
+        self.weight: torch.Tensor | None = None
+
+    def param_specs(self) -> list[ParamSpec]:
+        return [ParamSpec(self.name, (self.size,), "norm")]
+
+    def bind(self, get: Callable[[str], torch.Tensor]) -> None:
+        self.weight = get(self.name).to(torch.float32).contiguous()
+
+    def forward(self, x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        return self.add_forward(x, None, out_dtype)
+
+    def add_forward(self, residual: torch.Tensor, delta, out_dtype: torch.dtype,
+                    rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        n = residual.shape[0] if rows is None else rows.shape[0]
+        out = self.rt.empty((n, self.size), out_dtype)
+        deltas = delta if isinstance(delta, tuple) else (delta,)
+        ops.add_group_rmsnorm(out, residual, deltas, self.weight, self.groups, self.eps, self.rt.stream, rows=rows)
         return out

@@ -1,6 +1,7 @@
 """Random weights: a model folder (config.json, model.safetensors) from a configuration and a seed.
 
-Linear maps and the embedding are drawn from N(0, std), norm weights from 1 + N(0, norm_std);
+Linear maps and the embedding are drawn from N(0, std), norm weights from 1 + N(0, norm_std), bounds
+("unit") uniformly from (0, 1);
 each tensor has its own generator seeded by (seed, tensor name), so a tensor's values do not
 depend on which other tensors exist.  Values are rounded to the storage type once; whoever reads
 the folder sees the rounded values.
@@ -30,6 +31,8 @@ def random_tensor(spec: ParamSpec, seed: int, std: float, norm_std: float, dtype
     g.manual_seed(_tensor_seed(seed, spec.name))
     if spec.integer:
         return torch.randint(0, 2 ** 15, spec.shape, generator=g, device=device, dtype=torch.int32)
+    if spec.init == "unit":                        # a bound or a rate that lies inside (0, 1)
+        return torch.rand(spec.shape, generator=g, device=device, dtype=torch.float32).to(dtype)
     x = torch.randn(spec.shape, generator=g, device=device, dtype=torch.float32)
     if spec.init == "norm":
         x = 1.0 + norm_std * x
