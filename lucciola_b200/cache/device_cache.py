@@ -68,3 +68,9 @@ class DeviceCache:
         if pages:
             idx = torch.tensor(list(pages), dtype=torch.long, device=self.pools[group].device)
             self.pools[group][:, :, idx] = value
+
+    def poison_slots(self, slots: Sequence[int], value: float = float("nan")) -> None:
+        """Fill the state rows of these slots with a value that would show in any sum (for tests of slot reuse)."""
+        for st in self.states.values():
+            for slot in slots:
+                st[slot] = value

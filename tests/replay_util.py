@@ -118,10 +118,12 @@ def replay(runner, steps: list[dict], poison: bool = False) -> dict[tuple[str, i
                     r += 1
         for rid in s["end"]:
             tables = [list(runner.manager.block_table(rid, g)) for g in range(len(runner.groups))]
+            slot = runner.manager.slot(rid)
             runner.finish(rid)
-            if poison:                                     # what a freed page still holds must never matter
+            if poison:                                     # what a freed page or state slot still holds must never matter
                 for g, t in enumerate(tables):
                     runner.cache.poison_pages(g, [p for p in t if p >= 0])
+                runner.cache.poison_slots([slot])
         runner.manager.check_invariants()
     return out
 
