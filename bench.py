@@ -25,6 +25,10 @@ decode step of the whole batch.  The line printed at the end is one JSON object:
                                    pool with fewer pages than they need together, so that the scheduler preempts
               (--no-points skips them; --workloads chooses among them)
 
+`--design riruzen` measures another workload instead and leaves the default one alone: prefill and decode throughput of the
+Riruzen design (parallel blocks, alternating HGRN2 and latent-attention mixers) at layer sizes of real models, beside the Qwen3
+decoder of this engine at the same width, feed-forward size, head count and depth; one JSON line a (size, model), random weights.
+
 Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else from the
 fallback figures 6650 GB/s and 1590 TFLOP/s.  The timed work reads far more than the 126 MB of L2
 per step (weights alone are 16 GB), so no explicit L2 flush is made.
@@ -422,6 +426,151 @@ def time_attention_key_ranges() -> int:
     return 0
 
 
+# Layer sizes for --design: width, heads of 128, feed-forward and vocabulary of models of about 1.7 and 8 billion weights.  The
+# latent of the attention layers has 128 values (the head size up to which the tensor-core attention kernels go).
+DESIGN_SIZES = {
+    "w2048": dict(width=2048, heads=16, dim=128, ff=6144, q_rank=768, kv_rank=128, vocab=32000),
+    "w4096": dict(width=4096, heads=32, dim=128, ff=12288, q_rank=1536, kv_rank=128, vocab=32000),
+}
+
+
+def design_configs(size: dict, layers: int, positions: int) -> dict:
+    """The Riruzen configuration of these sizes (HGRN2 and latent attention in turn) and the Qwen3 one beside it."""
+    W, H, D = size["width"], size["heads"], size["dim"]
+    rec = {"type": "hgrn2", "mixer": {"heads": H, "dim": D, "vdim": D}, "mlp": {"kind": "dense", "ff": size["ff"]}}
+    att = {"type": "latent_attention", "mixer": {"heads": H, "dim": D, "vdim": D, "q_rank": size["q_rank"], "kv_rank": size["kv_rank"],
+                                                 "scale": D ** -0.5}, "mlp": {"kind": "dense", "ff": size["ff"]}}
+    riruzen = {"architecture": "Riruzen", "vocab": size["vocab"], "width": W, "max_positions": positions, "logit_scale": 1.0,
+               "norm": {"eps": 1e-6, "groups": 4}, "canon": {"taps": 4}, "layers": [rec if i % 2 == 0 else att for i in range(layers)]}
+    qwen3 = dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=W, num_attention_heads=H, num_key_value_heads=max(H // 4, 1), head_dim=D,
+                 intermediate_size=size["ff"], vocab_size=size["vocab"], max_position_embeddings=positions, tie_word_embeddings=True)
+    return {"riruzen": riruzen, "qwen3": qwen3}
+
+
+def design_costs(name: str, cfg: dict) -> dict:
+    """Weights a decode step reads, cache bytes a cached token and a live request cost a step, FLOPs of the products a token."""
+    if name == "qwen3":
+        L = cfg["num_hidden_layers"]
+        per_layer, weight_bytes, kv = model_bytes_and_flops(cfg, L)
+        weight_bytes -= cfg["vocab_size"] * cfg["hidden_size"] * 2 * 0          # the tied table is read once, by the head
+        return {"weight_bytes": weight_bytes, "token_bytes": kv, "request_bytes": 0, "flops_per_token": 2.0 * per_layer * L,
+                "attn_flops": lambda T: L * cfg["num_attention_heads"] * 4.0 * cfg["head_dim"] * (T * (T + 1) / 2)}
+    W = cfg["width"]
+    weights = token_bytes = request_bytes = 0
+    attn = []
+    for l in cfg["layers"]:
+        m = l["mixer"]
+        H, D, Vd = m["heads"], m["dim"], m["vdim"]
+        if l["type"] == "hgrn2":
+            weights += (2 * H * D + H * Vd) * W + W * H * Vd
+            request_bytes += 2 * 4 * H * D * Vd                                   # the state, read and written
+            attn.append(lambda T, H=H, D=D, Vd=Vd: 6.0 * T * H * D * Vd)
+        else:
+            r, c = m["q_rank"], m["kv_rank"]
+            weights += (r + c + H * Vd) * W + H * D * r + H * D * c + H * Vd * c + W * H * Vd
+            token_bytes += 2 * c
+            attn.append(lambda T, H=H, c=c: H * 4.0 * c * (T * (T + 1) / 2))
+        if l["mlp"]:
+            weights += 3 * l["mlp"]["ff"] * W
+        request_bytes += 2 * 2 * (cfg["canon"]["taps"] - 1) * W
+    return {"weight_bytes": 2 * (weights + cfg["vocab"] * W), "token_bytes": token_bytes, "request_bytes": request_bytes,
+            "flops_per_token": 2.0 * weights, "attn_flops": lambda T: sum(f(T) for f in attn)}
+
+
+def run_design(args) -> int:
+    """Prefill and decode of Riruzen beside Qwen3 at equal sizes (device-timed through the step function, with the
+    sampler; decode steps replayed from CUDA graphs as in serving).  One JSON line a (size, model)."""
+    import gc
+
+    import numpy as np
+    import torch
+
+    from lucciola_b200 import ops
+    from lucciola_b200.config import EngineOptions
+    from lucciola_b200.engine.load import build_runner_random
+    from lucciola_b200.engine.step import StepEntry
+    pk = peaks()
+    layers = args.layers or 8
+    ctx, T, page = min(args.context, 2048), args.prefill_tokens, 16
+    K, Wm = min(args.steps, 64), max(args.warmup, 3)
+    rng = np.random.default_rng(0)
+    sizes = [s for s in args.design_sizes.split(",") if s]
+    batches = [b for b in (1, 8, 64) if not args.profile or b == args.batch]
+    for sname in sizes:
+        for mname, cfg in design_configs(DESIGN_SIZES[sname], layers, max(ctx, T) + K + Wm + 64).items():
+            if args.design_models and mname not in args.design_models.split(","):
+                continue
+            cost = design_costs(mname, cfg)
+            V = cfg.get("vocab", cfg.get("vocab_size"))
+            pages = 64 * (-(-(ctx + K + Wm + 8) // page)) + -(-T // page) + 64
+            options = EngineOptions(dtype="bfloat16", block_size=page, max_blocks=pages, max_num_seqs=66, max_tokens_per_step=T + 64,
+                                    use_cuda_graph=not (args.no_graph or args.profile))
+            runner = build_runner_random(cfg, 0, options, std=0.02, num_pages=pages)
+            ev = lambda: torch.cuda.Event(enable_timing=True)
+            out = {"design": mname, "size": sname, "layers": layers, "dtype": "bf16", "data": "synthetic: random token ids, random weights"}
+            if args.profile == "prefill" or not args.profile:
+                times = []
+                for i in range(3 + (1 if args.profile else 5)):
+                    ids = rng.integers(0, V, size=T).tolist()
+                    a, b = ev(), ev()
+                    torch.cuda.synchronize()
+                    if args.profile and i == 3:
+                        torch.cuda.profiler.start()
+                    a.record()
+                    runner.step([StepEntry(("p", i), ids, [T - 1])])
+                    b.record()
+                    torch.cuda.synchronize()
+                    if args.profile and i == 3:
+                        torch.cuda.profiler.stop()
+                    runner.finish(("p", i))
+                    if i >= 3:
+                        times.append(a.elapsed_time(b))
+                ms = statistics.median(times)
+                flops = T * cost["flops_per_token"] + cost["attn_flops"](T)
+                out["prefill"] = {"tokens": T, "ms": round(ms, 3), "tokens_per_s": round(T / ms * 1e3, 1),
+                                  "frac_of_bf16_peak": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+            for B in batches:
+                if args.profile == "prefill":
+                    break
+                rids = [("d", B, j) for j in range(B)]
+                for r in rids:                                                # bring B requests to the context, untimed
+                    runner.step([StepEntry(r, rng.integers(0, V, size=ctx - K - Wm).tolist(), [])])
+                tokens = torch.empty(B, dtype=torch.int32, device=runner.device)
+
+                def one():
+                    logits = runner.step([StepEntry(r, [int(rng.integers(0, V))], [0]) for r in rids])
+                    ops.sample(tokens, logits, torch.cuda.current_stream().cuda_stream)
+                for _ in range(Wm):
+                    one()
+                launches0 = runner.kernel_launches()
+                a, b = ev(), ev()
+                torch.cuda.synchronize()
+                if args.profile:
+                    torch.cuda.profiler.start()
+                a.record()
+                for _ in range(1 if args.profile else K):
+                    one()
+                b.record()
+                torch.cuda.synchronize()
+                if args.profile:
+                    torch.cuda.profiler.stop()
+                steps = 1 if args.profile else K
+                ms = a.elapsed_time(b) / steps
+                mean_ctx = sum(runner.length(r) for r in rids) / B - steps / 2
+                step_bytes = cost["weight_bytes"] + B * (mean_ctx * cost["token_bytes"] + cost["request_bytes"])
+                out[f"decode_b{B}"] = {"context": int(mean_ctx), "ms_per_step": round(ms, 4), "tokens_per_s": round(B / ms * 1e3, 1),
+                                       "launches_per_step": (runner.kernel_launches() - launches0) // steps,
+                                       "frac_of_hbm_peak": round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
+                for r in rids:
+                    runner.finish(r)
+            out["device_error"] = ops.device_error()
+            print(json.dumps(out), flush=True)
+            del runner
+            gc.collect()
+            torch.cuda.empty_cache()
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -453,9 +602,17 @@ def main() -> int:
     ap.add_argument("--portion", type=int, default=512, help="tokens of the portion of a --profile mixed step")
     ap.add_argument("--time-kernel", choices=["attention_key_ranges"], default=None,
                     help="time one kernel alone over a grid of sizes, print a line of JSON a case, and exit")
+    ap.add_argument("--design", choices=["riruzen"], default=None,
+                    help="instead of the default workload: prefill and decode of this design beside the Qwen3 decoder at equal "
+                         "sizes (--design-sizes; --layers, default 8; --prefill-tokens; --context up to 2048; --profile decode|prefill "
+                         "with --batch runs one step between cudaProfilerStart/Stop)")
+    ap.add_argument("--design-sizes", default="w2048,w4096", help="which of %s" % ", ".join(sorted(DESIGN_SIZES)))
+    ap.add_argument("--design-models", default="", help="riruzen, qwen3 or both (empty)")
     args = ap.parse_args()
     if args.time_kernel == "attention_key_ranges":
         return time_attention_key_ranges()
+    if args.design:
+        return run_design(args)
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

@@ -113,6 +113,24 @@ __global__ void add_rmsnorm_row_kernel(TO* __restrict__ out, float* __restrict__
     store4(o + 4 * (q * nt + tid), make_float4(v[q].x * inv * w[q].x, v[q].y * inv * w[q].y, v[q].z * inv * w[q].z, v[q].w * inv * w[q].w));
 }
 
+// Short rows without a delta (the heads of a mixer's output, one row a head): a warp a row, eight rows a CTA.
+template <typename TO>
+__global__ void rmsnorm_short_rows_kernel(TO* __restrict__ out, const float* __restrict__ x, const float* __restrict__ weight,
+                                          int num_rows, int hidden, float eps) {
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= num_rows) return;
+  const float* r = x + (size_t)row * hidden;
+  float ss = 0.f;
+  for (int j = lane; j < hidden; j += 32) { const float v = r[j]; ss += v * v; }
+  ss = warp_sum(ss);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  TO* o = out + (size_t)row * hidden;
+  for (int j = lane; j < hidden; j += 32) o[j] = from_f32<TO>(r[j] * inv * weight[j]);
+}
+
 // RMSNorm in groups: the row is cut into `groups` equal consecutive parts and each part is divided by its own
 // sqrt(mean(part^2) + eps); the whole is multiplied by the weight.  Up to two deltas are added to the residual
 // stream first (in 32-bit, a then b), for blocks whose sublayers run side by side and leave their outputs unsummed.
@@ -258,6 +276,15 @@ LB_EXPORT int lb_add_rmsnorm(void* out, int out_dtype, float* residual, const vo
     if (hidden % cand == 0 && (hidden / cand) % 32 == 0 && hidden / cand >= 64 && hidden / cand <= 1024) { per = cand; threads = hidden / cand; break; }
   }
   const bool aligned = ((uintptr_t)out % 16 == 0) && ((uintptr_t)residual % 16 == 0) && ((uintptr_t)delta % 16 == 0) && ((uintptr_t)weight % 16 == 0);
+  if (delta == nullptr && rows == nullptr && hidden <= 512) {
+    // short rows: a warp a row, whatever their number (a row's sum must not depend on the batch)
+    LB_DISPATCH_DTYPE(out_dtype, TO, {
+      lb::launch(lb::rmsnorm_short_rows_kernel<TO>, dim3((num_rows + 7) / 8), dim3(256), 0, stream, (TO*)out, (const float*)residual,
+                 weight, num_rows, hidden, eps);
+    })
+    LB_CHECK_LAUNCH("add_rmsnorm");
+    return 0;
+  }
   LB_DISPATCH_DTYPE(delta_dtype, TD, {
     LB_DISPATCH_DTYPE(out_dtype, TO, {
       if (aligned && (per == 4 || per == 8 || per == 16)) {

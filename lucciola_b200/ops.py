@@ -41,6 +41,8 @@ _SIGNATURES = {
                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "lb_gated_recurrence": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+    "lb_gemm_heads_mma": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
+                          c_longlong, c_longlong, c_void_p, c_longlong, c_void_p],
     "lb_gemm_plain_batched": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong,
                               c_longlong, c_longlong, c_longlong, c_longlong, c_void_p, c_longlong, c_void_p],
     "lb_add_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
@@ -163,11 +165,14 @@ def scale_(x: torch.Tensor, factor: float, stream: int) -> None:
 
 
 def causal_taps(out: torch.Tensor, h: torch.Tensor, weight: torch.Tensor, state: torch.Tensor | None, step, stream: int) -> None:
-    """out_t = h_t + sum_j weight[:, j] * h_(t - taps + 1 + j) over each sequence's tokens in order; what lies before
-    a portion is read from state[slot] ([taps - 1, width], oldest first).  The state is not changed."""
+    """out_t = h_t + sum_j weight[j, :] * h_(t - taps + 1 + j) over each sequence's tokens in order (weight [taps, width],
+    oldest tap first); what lies before a portion is read from state[slot] ([taps - 1, width], oldest first).  The
+    state is not changed."""
     _check(out, "convolution output", h.dtype); _check(h, "convolution input"); _check(weight, "taps", torch.float32)
     T, W = h.shape
-    taps = weight.shape[1]
+    taps = weight.shape[0]
+    if weight.shape[1] != W:
+        raise KernelError(f"the taps are [{weight.shape[0]}, {weight.shape[1]}] for rows of {W}")
     if state is not None:
         _check(state, "convolution state", h.dtype)
     _call("lb_causal_taps", dtype_code(h.dtype), out.data_ptr(), h.data_ptr(), weight.data_ptr(), _ptr(state),
@@ -208,7 +213,8 @@ def gated_recurrence(pre: torch.Tensor, q_col: int, f_col: int, v_col: int, bias
 
 
 def gemm_heads(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int, gate: torch.Tensor | None = None) -> None:
-    """y[t, h, :] = x[t, h, :] . w[h]^T for w [heads, N, K], one product a head, 32-bit sums on the ordinary pipes.
+    """y[t, h, :] = x[t, h, :] . w[h]^T for w [heads, N, K], one product a head, 32-bit sums: bfloat16 operands with K
+    a multiple of 8 on the tensor cores, everything else on the ordinary pipes.
     With `gate` (float32 [T, >= heads * N], row-strided): y[t, h, n] *= sigmoid(gate[t, h * N + n]) before the rounding."""
     T, H, K = x.shape
     N = w.shape[1]
@@ -217,6 +223,10 @@ def gemm_heads(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int, g
         raise KernelError(f"per-head product shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
     if gate is not None and (gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape[0] != T or gate.shape[1] != H * N):
         raise KernelError("the gate must be float32 [T, heads * N] with unit column stride")
+    if (x.dtype == w.dtype == y.dtype == torch.bfloat16 and K % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+        _call("lb_gemm_heads_mma", y.data_ptr(), x.data_ptr(), w.data_ptr(), H, T, N, K, H * K, H * N, K, N * K, N, _ptr(gate),
+              gate.stride(0) if gate is not None else 0, stream)
+        return
     _call("lb_gemm_plain_batched", y.data_ptr(), dtype_code(y.dtype), x.data_ptr(), dtype_code(x.dtype), w.data_ptr(),
           dtype_code(w.dtype), H, T, N, K, H * K, H * N, K, N * K, N, _ptr(gate), gate.stride(0) if gate is not None else 0, stream)
 

@@ -22,13 +22,13 @@ class CausalTaps(Part):
         if taps < 1:
             raise ValueError(f"a convolution needs at least one tap, got {taps}")
         self.rt, self.name, self.width, self.taps = rt, name, width, int(taps)
-        self.weight: torch.Tensor | None = None     # float32 [width, taps]
+        self.weight: torch.Tensor | None = None     # float32 [taps, width]: the checkpoint's tensor, transposed
 
     def param_specs(self) -> list[ParamSpec]:
         return [ParamSpec(self.name, (self.width, self.taps), "linear")]
 
     def bind(self, get: Callable[[str], torch.Tensor]) -> None:
-        self.weight = get(self.name).to(torch.float32).contiguous()
+        self.weight = get(self.name).to(torch.float32).t().contiguous()
 
     def cache_request(self) -> Optional[StateSlot]:
         return StateSlot((self.taps - 1, self.width), self.rt.act_dtype) if self.taps > 1 else None

@@ -13,6 +13,11 @@ are both the cached latents, through the same paged attention kernels as grouped
 prompts and for decoding alike.  The three maps that read u (W_dq | W_dkv | W_g) are one product with
 32-bit output; the two norms and the write into the pages are one kernel; the per-head maps are one
 batched product each, the second with the sigmoid gate in its epilogue.
+
+Where it costs no more multiplications than the two maps apart (kv_rank * q_rank <= dim * (q_rank + kv_rank):
+latents no wider than about a head), the query's two maps are multiplied out once when the weights are bound,
+W_qc[h] = W_uk[h]^T W_uq[h] ([kv_rank, q_rank], formed in 32-bit), and the query in latent space is one product
+of the normed query latent with the stacked W_qc.
 """
 from __future__ import annotations
 
@@ -42,6 +47,9 @@ class LatentAttention(Mixer):
         self.kv_norm_w: torch.Tensor | None = None
         self.uk_t: torch.Tensor | None = None       # [heads, kv_rank, dim]: W_uk[h]^T, the key map moved to the query
         self.uv: torch.Tensor | None = None         # [heads, vdim, kv_rank]
+        # the query's two maps as one, where that is no more work (see the module's text)
+        self.merge_query_maps = kv_rank * q_rank <= dim * (q_rank + kv_rank)
+        self.qc: Linear | None = None               # [heads * kv_rank, q_rank] when merged
 
     def children(self) -> list[Part]:
         return [self.down, self.uq, self.o]
@@ -57,6 +65,16 @@ class LatentAttention(Mixer):
         self.kv_norm_w = get(f"{p}.dkv.norm").to(torch.float32).contiguous()
         self.uk_t = get(f"{p}.uk").view(self.heads, self.dim, self.kv_rank).transpose(1, 2).contiguous()
         self.uv = get(f"{p}.uv").view(self.heads, self.vdim, self.kv_rank).contiguous()
+
+    def bind_all(self, get) -> None:
+        super().bind_all(get)
+        if self.merge_query_maps:
+            uq = self.uq.weight.view(self.heads, self.dim, self.q_rank)
+            merged = torch.bmm(self.uk_t.float(), uq.float()).reshape(self.heads * self.kv_rank, self.q_rank)
+            self.qc = Linear(self.rt, f"{self.prefix}.uk^T.uq", self.q_rank, self.heads * self.kv_rank)
+            self.qc.bind_tensor(merged.to(self.uq.weight.dtype).contiguous())
+            self.uq.weight = None                   # the two maps are not needed apart
+            self.uk_t = None
 
     def cache_request(self) -> KVPages:
         return KVPages(1, self.kv_rank, 0, shared=True)
@@ -85,9 +103,12 @@ class LatentAttention(Mixer):
         c_q = rt.empty((T, self.q_rank))
         ops.latent_norm(pre, 0, self.q_rank, self.q_rank, self.kv_rank, self.q_norm_w, self.kv_norm_w, c_q, cache.k,
                         step, table, cache.page_size, self.eps, rt.stream)
-        q = self.uq.forward(c_q).view(T, H, self.dim)
-        q_lat = rt.empty((T, H, self.kv_rank))
-        ops.gemm_heads(q_lat, q, self.uk_t, rt.stream)                       # the head's key map, applied to the query
+        if self.qc is not None:
+            q_lat = self.qc.forward(c_q).view(T, H, self.kv_rank)
+        else:
+            q = self.uq.forward(c_q).view(T, H, self.dim)
+            q_lat = rt.empty((T, H, self.kv_rank))
+            ops.gemm_heads(q_lat, q, self.uk_t, rt.stream)                   # the head's key map, applied to the query
         mix = rt.empty((T, H, self.kv_rank))
         ops.attention(q_lat, mix, cache.k, cache.v, step, cache.group, H, 1, self.kv_rank, cache.page_size, 0,
                       self.scale, rt.stream, plan=step.plans.get(self.plan_key()))

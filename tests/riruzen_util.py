@@ -28,12 +28,14 @@ def _config(vocab, width, positions, logit_scale, eps, groups, taps, layers):
 # Q: everything that can be 1 is 1 (groups, taps, heads), one layer of each kind.
 # R: sizes at which the bfloat16 engine takes its tensor-core paths (multiples of 64 and 128), two taps.
 # S: a recurrence only (no pages at all), five taps, many small heads.
+# In P and R the last attention layer has a latent so much wider than a head that the engine keeps the query's two
+# maps apart; in the other attention layers it multiplies them out.
 CONFIGS = {
     "P": _config(211, 72, 640, 0.5, 1e-6, 3, 4, [_latent(3, 20, 12, 36, 28, 0.3, 100), _latent(2, 16, 24, 24, 40, 0.21, None),
-                                                 _hgrn2(2, 20, 40, 56), _latent(5, 8, 8, 16, 16, 0.4, 88), _hgrn2(3, 36, 12, None)]),
+                                                 _hgrn2(2, 20, 40, 56), _latent(5, 8, 8, 32, 48, 0.4, 88), _hgrn2(3, 36, 12, None)]),
     "Q": _config(97, 40, 300, 1.0, 1e-5, 1, 1, [_hgrn2(1, 40, 40, 64), _latent(1, 32, 32, 40, 24, 0.17, 64)]),
     "R": _config(331, 256, 1024, 0.125, 2e-6, 2, 2, [_hgrn2(2, 128, 64, 512), _latent(4, 64, 64, 128, 128, 0.125, 512),
-                                                     _hgrn2(4, 64, 128, 256), _latent(8, 32, 48, 64, 64, 0.18, 256)]),
+                                                     _hgrn2(4, 64, 128, 256), _latent(8, 32, 48, 64, 128, 0.18, 256)]),
     "S": _config(150, 48, 400, 2.0, 1e-5, 4, 5, [_hgrn2(6, 8, 8, 96), _hgrn2(3, 12, 16, None)]),
 }
 PAGE = {"P": 16, "Q": 8, "R": 16, "S": 16}
