@@ -40,7 +40,7 @@ _SIGNATURES = {
     "lb_latent_norm": [c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                        c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
     "lb_gated_recurrence": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                            c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "lb_gemm_heads_mma": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_longlong, c_longlong,
                           c_longlong, c_longlong, c_void_p, c_longlong, c_void_p],
     "lb_gemm_plain_batched": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_longlong,
@@ -200,16 +200,19 @@ def latent_norm(pre: torch.Tensor, q_col: int, kv_col: int, q_rank: int, kv_rank
 
 
 def gated_recurrence(pre: torch.Tensor, q_col: int, f_col: int, v_col: int, bias: torch.Tensor, lower: torch.Tensor,
-                     state: torch.Tensor, out: torch.Tensor, step, heads: int, dim: int, vdim: int, stream: int) -> None:
+                     state: torch.Tensor, out: torch.Tensor, step, heads: int, dim: int, vdim: int, stream: int,
+                     max_tokens_a_seq: int = 0) -> None:
     """The HGRN2 recurrence over this step's tokens: per head S <- diag(f) S + (1 - f) v^T, out = S^T q with
     q = silu(pre[:, q_col..]), f = lower + (1 - lower) sigmoid(pre[:, f_col..] + bias), v = pre[:, v_col..];
-    state [slots + 1, heads, dim, vdim] float32 is read and written at each sequence's slot; out [T, heads * vdim] float32."""
+    state [slots + 1, heads, dim, vdim] float32 is read and written at each sequence's slot; out [T, heads * vdim] float32.
+    `max_tokens_a_seq`: the most tokens any sequence brings, if the host knows it (0: unknown); steps of a few tokens a
+    sequence run in a kernel made for them, with the same sums in the same order."""
     _check(pre, "input projections", torch.float32); _check(bias, "gate bias", torch.float32)
     _check(lower, "lower bound", torch.float32); _check(state, "recurrent state", torch.float32)
     _check(out, "recurrence output", torch.float32)
     _call("lb_gated_recurrence", pre.data_ptr(), pre.stride(0), q_col, f_col, v_col, bias.data_ptr(), lower.data_ptr(),
           state.data_ptr(), out.data_ptr(), step.cu_tokens.data_ptr(), step.state_slots.data_ptr(), step.num_seqs,
-          heads, dim, vdim, stream)
+          heads, dim, vdim, max_tokens_a_seq, stream)
 
 
 def gemm_heads(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int, gate: torch.Tensor | None = None) -> None:

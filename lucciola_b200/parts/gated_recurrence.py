@@ -55,7 +55,8 @@ class GatedLinearRecurrence(Mixer):
             raise ops.KernelError("a recurrent mixer has no cache another call could have written")
         pre = self.qfv.forward(u, out_dtype=torch.float32)                    # [T, 2 * H * dim + H * vdim]
         o = rt.empty((T, H * self.vdim), torch.float32)
-        ops.gated_recurrence(pre, 0, n, 2 * n, self.bias, self.lower, cache.state, o, step, H, self.dim, self.vdim, rt.stream)
+        ops.gated_recurrence(pre, 0, n, 2 * n, self.bias, self.lower, cache.state, o, step, H, self.dim, self.vdim, rt.stream,
+                             max_tokens_a_seq=step.max_q_len)
         normed = rt.empty((T * H, self.vdim))
         ops.add_rmsnorm(normed, o.view(T * H, self.vdim), None, self.norm_w, self.eps, rt.stream)
         return self.o.forward(normed.view(T, H * self.vdim))

@@ -91,7 +91,7 @@ def test_causal_taps_over_portions_of_several_sequences(taps, dtype):
         assert torch.equal(state[1], torch.zeros_like(state[1])) and torch.equal(state[2].cpu(), full[0][-(taps - 1):].cpu())
 
 
-@pytest.mark.parametrize("heads,dim,vdim", [(2, 20, 40), (1, 40, 40), (3, 36, 12), (2, 128, 64), (4, 64, 128), (6, 8, 8), (1, 200, 33), (1, 300, 5)])
+@pytest.mark.parametrize("heads,dim,vdim", [(2, 20, 40), (1, 40, 40), (3, 36, 12), (2, 128, 64), (4, 64, 128), (6, 8, 8), (1, 200, 33), (1, 256, 5)])
 def test_gated_recurrence_alone(heads, dim, vdim):
     """Two sequences in unequal portions, against the plain recurrence with the output map left out (identity)."""
     from lucciola_b200 import ops
@@ -112,7 +112,9 @@ def test_gated_recurrence_alone(heads, dim, vdim):
         lens = [min(sizes[i], lens_total[i] - at[i]) for i in live]
         x = torch.cat([pre[i][at[i]:at[i] + k] for i, k in zip(live, lens)])
         out = torch.empty(x.shape[0], heads * vdim, device=DEV)
-        ops.gated_recurrence(x, 0, n, 2 * n, bias, lower, state, out, batch_of(lens, [slots[i] for i in live]), heads, dim, vdim, stream())
+        # steps of a few tokens a sequence, when the caller says so, run in a kernel of their own
+        ops.gated_recurrence(x, 0, n, 2 * n, bias, lower, state, out, batch_of(lens, [slots[i] for i in live]), heads, dim, vdim, stream(),
+                             max_tokens_a_seq=max(lens) if max(lens) <= 3 else 0)
         o = 0
         for i, k in zip(live, lens):
             got[i].append(out[o:o + k]); o += k; at[i] += k
