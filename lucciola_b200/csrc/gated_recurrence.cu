@@ -198,8 +198,8 @@ static cudaError_t launch_gated_recurrence(const GatedRecurrenceParams& p, int n
 // warp order: the sums and their order are those of the kernel above, so both give the same bits.
 constexpr int GR_SHORT_TC = 4;
 
-template <int DS>
-__global__ void gated_recurrence_short_kernel(GatedRecurrenceParams p) {
+template <int DS, int MAX_THREADS>
+__global__ void __launch_bounds__(MAX_THREADS) gated_recurrence_short_kernel(GatedRecurrenceParams p) {
   extern __shared__ __align__(16) float smem[];
   pdl_trigger();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -274,11 +274,17 @@ __global__ void gated_recurrence_short_kernel(GatedRecurrenceParams p) {
   }
 }
 
-template <int DS>
+template <int DS, int MAX_THREADS = 256>
 static cudaError_t launch_gated_recurrence_short(const GatedRecurrenceParams& p, int num_seqs, cudaStream_t stream) {
   const int nwarps = (p.dim + DS - 1) / DS;
-  const size_t smem = (size_t)GR_SHORT_TC * (2 * nwarps * DS + 32 + nwarps * 32) * sizeof(float);      // at most 18 KB
-  return launch(gated_recurrence_short_kernel<DS>, dim3((p.vdim + 31) / 32, p.heads, num_seqs), dim3(nwarps * 32), smem, stream, p);
+  const size_t smem = (size_t)GR_SHORT_TC * (2 * nwarps * DS + 32 + nwarps * 32) * sizeof(float);      // up to 50 KB (32 warps)
+  static size_t allowed = 48 * 1024;
+  if (smem > allowed) {
+    const cudaError_t e = cudaFuncSetAttribute(gated_recurrence_short_kernel<DS, MAX_THREADS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    allowed = smem;
+  }
+  return launch(gated_recurrence_short_kernel<DS, MAX_THREADS>, dim3((p.vdim + 31) / 32, p.heads, num_seqs), dim3(nwarps * 32), smem, stream, p);
 }
 
 }  // namespace lb
@@ -287,15 +293,18 @@ LB_EXPORT int lb_gated_recurrence(const float* pre, long long ld, int q_col, int
                                   const float* lower, float* state, float* out, const int* cu_tokens, const int* slots,
                                   int num_seqs, int heads, int dim, int vdim, int max_tokens_a_seq, cudaStream_t stream) {
   LB_CHECK_ARG(pre && bias && lower && state && out && cu_tokens && slots, "gated_recurrence: null argument");
-  LB_CHECK_ARG(num_seqs >= 0 && heads > 0 && heads <= 65535 && dim > 0 && dim <= 256 && vdim > 0 && num_seqs <= 65535,
-               "gated_recurrence: bad sizes seqs=%d heads=%d dim=%d vdim=%d (dim at most 256: a warp keeps at most 32 rows of the state in registers)", num_seqs, heads, dim, vdim);
+  LB_CHECK_ARG(num_seqs >= 0 && heads > 0 && heads <= 65535 && dim > 0 && dim <= 1024 && vdim > 0 && num_seqs <= 65535,
+               "gated_recurrence: bad sizes seqs=%d heads=%d dim=%d vdim=%d (dim at most 1024)", num_seqs, heads, dim, vdim);
   if (num_seqs == 0) return 0;
   lb::GatedRecurrenceParams p;
   p.pre = pre; p.ld = ld; p.q_col = q_col; p.f_col = f_col; p.v_col = v_col; p.bias = bias; p.lower = lower;
   p.state = state; p.out = out; p.cu_tokens = cu_tokens; p.slots = slots; p.heads = heads; p.dim = dim; p.vdim = vdim;
   cudaError_t e;
-  // rows of the state a warp keeps: as few as give at most 8 warps
-  if (max_tokens_a_seq > 0 && max_tokens_a_seq <= lb::GR_SHORT_TC) {
+  // rows of the state a warp keeps: as few as give at most 8 warps.  Heads of more than 256 rows: 32 rows a warp and
+  // up to 32 warps, in the kernel without feeding warps whatever the step (the other would need more registers than a
+  // CTA of that size can have).
+  if (dim > 256) e = lb::launch_gated_recurrence_short<32, 1024>(p, num_seqs, stream);
+  else if (max_tokens_a_seq > 0 && max_tokens_a_seq <= lb::GR_SHORT_TC) {
     if (dim <= 32) e = lb::launch_gated_recurrence_short<4>(p, num_seqs, stream);
     else if (dim <= 64) e = lb::launch_gated_recurrence_short<8>(p, num_seqs, stream);
     else if (dim <= 128) e = lb::launch_gated_recurrence_short<16>(p, num_seqs, stream);

@@ -136,10 +136,12 @@ __global__ void rmsnorm_short_rows_kernel(TO* __restrict__ out, const float* __r
 // stream first (in 32-bit, a then b), for blocks whose sublayers run side by side and leave their outputs unsummed.
 // A group is walked by `wpg` warps; the partial sums of a group's warps are added in warp order, so a row's result
 // does not depend on the batch.  The row is read from global memory for the sums and again (from cache) for the output.
-template <typename TD, typename TO>
+template <typename TD, typename TO, int EPL>
 __global__ void add_group_rmsnorm_kernel(TO* __restrict__ out, float* __restrict__ residual, const TD* __restrict__ delta_a,
                                          const TD* __restrict__ delta_b, const float* __restrict__ weight,
                                          const int* __restrict__ rows, int hidden, int groups, int wpg, float eps) {
+  // EPL > 0: a lane has at most EPL elements of a group and keeps them in registers between the sum and the output
+  // (all loads issued before any is used); EPL == 0: any size, the row is read again (from cache) for the output.
   __shared__ float part[32];
   pdl_trigger();
   pdl_wait();
@@ -154,17 +156,41 @@ __global__ void add_group_rmsnorm_kernel(TO* __restrict__ out, float* __restrict
   const int gsize = hidden / groups;
   const int per_round = nwarps / wpg;                 // groups worked on at a time
   const int seg = warp % wpg;
+  constexpr int NV = EPL > 0 ? EPL : 1;
   for (int g0 = 0; g0 < groups; g0 += per_round) {
     const int g = g0 + warp / wpg;
     float ss = 0.f;
+    float v[NV];
     if (g < groups) {
-      for (int j = seg * 32 + lane; j < gsize; j += wpg * 32) {
-        const int c = g * gsize + j;
-        float v = r[c];
-        if (da) v += to_f32(da[c]);
-        if (db) v += to_f32(db[c]);
-        if (update) r[c] = v;
-        ss += v * v;
+      if (EPL > 0) {
+        float x[NV], ya[NV], yb[NV];
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+          const int j = seg * 32 + lane + k * wpg * 32, c = g * gsize + j;
+          const bool in = j < gsize;
+          x[k] = in ? r[c] : 0.f;
+          ya[k] = (in && da) ? to_f32(da[c]) : 0.f;
+          yb[k] = (in && db) ? to_f32(db[c]) : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+          const int j = seg * 32 + lane + k * wpg * 32, c = g * gsize + j;
+          float t = x[k];
+          if (da) t += ya[k];
+          if (db) t += yb[k];
+          v[k] = t;
+          if (update && j < gsize) r[c] = t;
+          ss += t * t;
+        }
+      } else {
+        for (int j = seg * 32 + lane; j < gsize; j += wpg * 32) {
+          const int c = g * gsize + j;
+          float t = r[c];
+          if (da) t += to_f32(da[c]);
+          if (db) t += to_f32(db[c]);
+          if (update) r[c] = t;
+          ss += t * t;
+        }
       }
     }
     ss = warp_sum(ss);
@@ -175,14 +201,22 @@ __global__ void add_group_rmsnorm_kernel(TO* __restrict__ out, float* __restrict
       float tot = 0.f;
       for (int k = 0; k < wpg; ++k) tot += part[(warp / wpg) * wpg + k];
       const float inv = 1.f / sqrtf(tot / (float)gsize + eps);
-      for (int j = seg * 32 + lane; j < gsize; j += wpg * 32) {
-        const int c = g * gsize + j;
-        float v = r[c];                               // own earlier write, or the untouched row
-        if (!update) {
-          if (da) v += to_f32(da[c]);
-          if (db) v += to_f32(db[c]);
+      if (EPL > 0) {
+#pragma unroll
+        for (int k = 0; k < NV; ++k) {
+          const int j = seg * 32 + lane + k * wpg * 32, c = g * gsize + j;
+          if (j < gsize) o[c] = from_f32<TO>(v[k] * inv * weight[c]);
         }
-        o[c] = from_f32<TO>(v * inv * weight[c]);
+      } else {
+        for (int j = seg * 32 + lane; j < gsize; j += wpg * 32) {
+          const int c = g * gsize + j;
+          float t = r[c];                             // own earlier write, or the untouched row
+          if (!update) {
+            if (da) t += to_f32(da[c]);
+            if (db) t += to_f32(db[c]);
+          }
+          o[c] = from_f32<TO>(t * inv * weight[c]);
+        }
       }
     }
   }
@@ -209,10 +243,18 @@ LB_EXPORT int lb_add_group_rmsnorm(void* out, int out_dtype, float* residual, co
   if (per_round > groups) per_round = groups;
   if (per_round < 1) per_round = 1;
   const int warps = wpg * per_round;
+  const int per_lane = (hidden / groups + wpg * 32 - 1) / (wpg * 32);      // elements of a group a lane has
   LB_DISPATCH_DTYPE(delta_dtype, TD, {
     LB_DISPATCH_DTYPE(out_dtype, TO, {
-      lb::launch(lb::add_group_rmsnorm_kernel<TD, TO>, dim3(num_rows), dim3(warps * 32), 0, stream, (TO*)out, residual,
-                 (const TD*)delta_a, (const TD*)delta_b, weight, rows, hidden, groups, wpg, eps);
+      // few rows (decoding): the variant that keeps a lane's elements in registers and issues all loads at once; many
+      // rows keep the SMs busy without that and run faster in the looping variant.  Both add the same terms in the same
+      // order, so the choice never shows in a result.
+      if (per_lane <= 8 && num_rows <= 256)
+        lb::launch(lb::add_group_rmsnorm_kernel<TD, TO, 8>, dim3(num_rows), dim3(warps * 32), 0, stream, (TO*)out, residual,
+                   (const TD*)delta_a, (const TD*)delta_b, weight, rows, hidden, groups, wpg, eps);
+      else
+        lb::launch(lb::add_group_rmsnorm_kernel<TD, TO, 0>, dim3(num_rows), dim3(warps * 32), 0, stream, (TO*)out, residual,
+                   (const TD*)delta_a, (const TD*)delta_b, weight, rows, hidden, groups, wpg, eps);
     })
   })
   LB_CHECK_LAUNCH("add_group_rmsnorm");

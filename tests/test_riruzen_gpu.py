@@ -91,7 +91,7 @@ def test_causal_taps_over_portions_of_several_sequences(taps, dtype):
         assert torch.equal(state[1], torch.zeros_like(state[1])) and torch.equal(state[2].cpu(), full[0][-(taps - 1):].cpu())
 
 
-@pytest.mark.parametrize("heads,dim,vdim", [(2, 20, 40), (1, 40, 40), (3, 36, 12), (2, 128, 64), (4, 64, 128), (6, 8, 8), (1, 200, 33), (1, 256, 5)])
+@pytest.mark.parametrize("heads,dim,vdim", [(2, 20, 40), (1, 40, 40), (3, 36, 12), (2, 128, 64), (4, 64, 128), (6, 8, 8), (1, 200, 33), (1, 256, 5), (1, 300, 40), (1, 1000, 8)])
 def test_gated_recurrence_alone(heads, dim, vdim):
     """Two sequences in unequal portions, against the plain recurrence with the output map left out (identity)."""
     from lucciola_b200 import ops
