@@ -470,3 +470,70 @@ def test_generation_under_page_pressure_recomputes_the_state(models):
     got = tight.generate(prompts, params)
     assert got == want
     assert tight.stats()["preemptions"] > 0 and roomy.stats()["preemptions"] == 0
+
+
+# ---- the programs ---------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype,graphs", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
+def test_trace_run_program(models, tmp_path, dtype, graphs):
+    """bin/trace_run as a user runs it on a Riruzen folder: the model is chosen by config.json, steps come on standard
+    input, <step>.f32 files go out; six requests through its four state slots."""
+    import json
+    import subprocess
+    import sys
+
+    import numpy as np
+
+    from conftest import ROOT
+    name = "P"
+    cfg, w, folder = models[name]
+    reqs = {f"t{i}": rz.tokens(cfg, n, salt=61) for i, n in enumerate((70, 33, 90, 5, 64, 41))}
+    steps = ru.mixed(reqs, seed=5, max_live=4)
+    out = tmp_path / "out"
+    p = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out),
+                        "--max-tokens", str(ru.max_live_tokens(steps))] + (["--cuda-graph"] if graphs else []),
+                       input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert [l for l in p.stdout.splitlines() if l.startswith("done")] == [f"done {s['step']}" for s in steps]
+    got, held = {}, {}
+    for s in steps:
+        wanted = sum(len(e["want"]) for e in s["entries"])
+        f = out / f"{s['step']}.f32"
+        assert f.exists() == (wanted > 0)
+        rows = np.fromfile(f, dtype="<f4").reshape(wanted, cfg["vocab"]) if wanted else None
+        r = 0
+        for e in s["entries"]:
+            start = held.get(e["id"], 0)
+            for k in e["want"]:
+                got[(e["id"], start + k)] = torch.from_numpy(rows[r].astype(np.float64)); r += 1
+            held[e["id"]] = start + len(e["tokens"])
+    rz.compare(got, name, cfg, w, reqs, dtype)
+
+
+def test_chat_program_and_random_model_program(tmp_path):
+    """bin/lucciola_random_model writes a Riruzen folder from a config.json; bin/lucciola_chat generates from it, and
+    its greedy tokens are the plain implementation's."""
+    import json
+    import subprocess
+    import sys
+
+    from conftest import ROOT
+    from lucciola_b200.weights.safetensors_io import SafetensorsFile
+    cfg = rz.CONFIGS["Q"]
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    folder = tmp_path / "model"
+    p = subprocess.run([sys.executable, str(ROOT / "bin" / "lucciola_random_model"), "--config", str(tmp_path / "config.json"), "--seed", "3",
+                        "--out", str(folder), "--std", "0.3", "--norm-std", "0.1"], capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr[-2000:]
+    prompt = rz.tokens(cfg, 19, salt=71)
+    p = subprocess.run([sys.executable, str(ROOT / "bin" / "lucciola_chat"), "--model", str(folder), "--dtype", "float32", "--max-blocks", "32",
+                        "--block-size", "8", "--max-new-tokens", "5", "--ignore-eos", "--prompt-ids", " ".join(map(str, prompt))],
+                       capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    out = [int(x) for x in p.stdout.split()[-5:]]
+    f = SafetensorsFile(folder / "model.safetensors")
+    w = {n: f.get(n).clone() for n in f.names()}
+    ids = list(prompt)
+    for tok in out:
+        row = plain.PlainRiruzen(cfg, w).forward(ids)[-1]
+        assert row.max() - row[tok] <= 1e-4 * row.abs().max(), (tok, int(row.argmax()))
+        ids.append(tok)
