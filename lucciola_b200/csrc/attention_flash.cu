@@ -48,6 +48,8 @@ struct FlashParams {
   int cluster;                              // > 0: the splits of a tile form a cluster of this size and combine through shared memory
   int num_q_heads, num_kv_heads, head_dim, group, page_size, page_shift, window, splits;   // page_shift: log2(page_size) or -1
   float scale_log2;                         // scale * log2(e)
+  int kv_share;                             // >= 1: the cache has num_kv_heads / kv_share heads, and kv head j of this launch
+                                            // reads cache head j / kv_share (several groups of query heads on one cached head)
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
@@ -257,8 +259,8 @@ flash_attention_kernel(FlashParams p) {
   const int ld_row = tid / CHUNKS, ld_chunk = tid % CHUNKS;
   const bool ld_col_valid = ld_chunk * 8 < d;
   const uint32_t ld_smem = tile_offset<DP>(ld_row, ld_chunk);
-  const size_t head_off = (size_t)kvh * p.page_size * d + ld_chunk * 8;
-  const size_t page_stride = (size_t)p.num_kv_heads * p.page_size * d;
+  const size_t head_off = (size_t)(kvh / p.kv_share) * p.page_size * d + ld_chunk * 8;
+  const size_t page_stride = (size_t)(p.num_kv_heads / p.kv_share) * p.page_size * d;
   auto load_stage = [&](int stage_idx) {
     const int buf = stage_idx % STAGES;
     const int kbase = kbeg + stage_idx * FA_KEYS + ld_row;
@@ -568,8 +570,8 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
       const int key0 = kbeg + st * FA_KEYS + box * box_keys;
       int page = -1;
       if (active && st < num_stages && key0 < kend) page = bt[key0 >> p.page_shift];
-      if (page < 0) return kvh * p.page_size;                                        // page 0: masked whatever it holds
-      return (page * p.num_kv_heads + kvh) * p.page_size + (key0 & (p.page_size - 1));
+      if (page < 0) return (kvh / p.kv_share) * p.page_size;                         // page 0: masked whatever it holds
+      return (page * (p.num_kv_heads / p.kv_share) + kvh / p.kv_share) * p.page_size + (key0 & (p.page_size - 1));
     };
     int row = row_of(0);                            // the tables were written before the step began
     auto fetch = [&](int st) {
@@ -890,13 +892,17 @@ LB_EXPORT long long lb_attention_flash_workspace(int num_tiles, int num_kv_heads
 
 // q, out: [T, nq, d] bfloat16.  tiles: [num_tiles] of {first token, tokens, request index, 0} with
 // tokens * (nq / nkv) <= part_rows <= 64.  workspace: float32, needed when splits > 1.
+// kv_share >= 1: the pools hold num_kv_heads / kv_share heads and kv head j reads pool head j / kv_share, so that
+// many query heads on one cached head can be cut into groups of at most 16 (the tiles of the decode kernels).
 LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, const void* v_cache,
                                  const int* positions, const int* block_table, const void* tiles, int num_tiles,
                                  int num_q_heads, int num_kv_heads, int head_dim, int page_size, int max_pages,
                                  int num_pages, int window, float scale, int splits, int part_rows, float* workspace,
-                                 long long workspace_elems, cudaStream_t stream) {
+                                 long long workspace_elems, int kv_share, cudaStream_t stream) {
   LB_CHECK_ARG(num_q_heads > 0 && num_kv_heads > 0 && num_q_heads % num_kv_heads == 0,
                "attention_flash: %d query heads are not a multiple of %d kv heads", num_q_heads, num_kv_heads);
+  LB_CHECK_ARG(kv_share >= 1 && num_kv_heads % kv_share == 0, "attention_flash: %d kv heads cannot share cached heads %d by %d",
+               num_kv_heads, kv_share, kv_share);
   const int group = num_q_heads / num_kv_heads;
   LB_CHECK_ARG(group <= lb::FA_ROWS, "attention_flash: %d query heads per kv head, at most %d", group, lb::FA_ROWS);
   LB_CHECK_ARG(head_dim >= 8 && head_dim <= 128 && head_dim % 8 == 0,
@@ -912,7 +918,7 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
   const int page_shift = lb::log2_exact(page_size);
   // Decoded tokens over pages of 8 to 128 keys: the kernel whose fifth warp fetches by TMA.  num_pages <= 0 keeps it off.
   const bool by_tma = part_rows <= 16 && num_pages > 0 && page_shift >= 3 && page_size <= 128 &&
-                      (long long)num_pages * num_kv_heads * page_size < (1ll << 31);
+                      (long long)num_pages * (num_kv_heads / kv_share) * page_size < (1ll << 31);
   // Up to 8 splits (a power of two) of tiles of at most 16 rows combine inside a thread-block cluster; the TMA kernel
   // also takes clusters of 16 (a size the launch has to ask for: not every GPU schedules it).
   const bool may_cluster = part_rows <= 16 && splits <= (by_tma ? 16 : 8) && !force_workspace;
@@ -928,6 +934,7 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
   p.page_size = page_size; p.window = window; p.splits = splits;
   p.page_shift = page_shift;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.kv_share = kv_share;
   dim3 grid(num_tiles, num_kv_heads, splits);
   const int dp = head_dim <= 64 ? 64 : 128;
   const int smem = part_rows <= 16 ? (lb::FA_ROWS + 2 * lb::FA_STAGES * lb::FA_KEYS) * dp * 2   // query tile + 3 stages
@@ -937,7 +944,7 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
   p.cluster = clustered ? splits : 0;
   if (by_tma) {
     CUtensorMap mk, mv;
-    const long long pool_rows = (long long)num_pages * num_kv_heads * page_size;
+    const long long pool_rows = (long long)num_pages * (num_kv_heads / kv_share) * page_size;
     const int box = page_size < lb::FA_KEYS ? page_size : lb::FA_KEYS;
     if (!lb::fd_pool_map(&mk, k_cache, pool_rows, head_dim, box) || !lb::fd_pool_map(&mv, v_cache, pool_rows, head_dim, box)) {
       lb::set_error("attention_flash: cuTensorMapEncodeTiled failed (pool of %lld rows of %d)", pool_rows, head_dim);

@@ -62,7 +62,7 @@ _SIGNATURES = {
     "lb_zero_rows": [c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p],
     "lb_gemm_tcgen05_heads": [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p],
     "lb_attention_flash": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                           c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_void_p],
+                           c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p],
     "lb_attention_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                              c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong, c_void_p],
     "lb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
@@ -600,8 +600,10 @@ def attention_wide_clusters(head_dim: int) -> int:
 def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     positions: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor, max_rows: int,
                     num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
-                    splits: int, stream: int, force_workspace: bool = False, tma: bool = True) -> None:
+                    splits: int, stream: int, force_workspace: bool = False, tma: bool = True, kv_share: int = 1) -> None:
     """Tensor-core attention over pages.  tiles: int32 [n, 4] of (first token, tokens, request index, 0).
+    `kv_share` > 1: the pools hold num_kv_heads / kv_share heads, and kv head j of this call reads pool head j // kv_share
+    (many query heads on one cached head, cut into groups of at most 16 so that decoded tokens fit the decode kernel's tiles).
     `force_workspace` sends the partial results of the splits through the workspace and the combining
     kernel even where a cluster could combine them.  Tiles of at most 16 query rows (decoded tokens) over pages of
     8 to 128 tokens run in the kernel whose keys and values a warp of its own fetches by TMA; `tma=False` keeps them
@@ -621,7 +623,7 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     _call("lb_attention_flash", q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
           positions.data_ptr(), block_table.data_ptr(), tiles.data_ptr(), n, num_q_heads, num_kv_heads, head_dim,
           page_size, block_table.shape[1], k_cache.shape[0] if tma else 0, window, scale,
-          -splits if force_workspace else splits, max_rows, _ptr(ws), ws_elems, stream)
+          -splits if force_workspace else splits, max_rows, _ptr(ws), ws_elems, kv_share, stream)
 
 
 def attention_tcgen05_ok(q: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
@@ -678,12 +680,14 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
 
 def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step, group: int,
               num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
-              stream: int, plan=None) -> None:
+              stream: int, plan=None, kv_share: int = 1) -> None:
     """Causal attention of this step's queries over the pages of their requests.  With a `plan` (tile lists
     by kind on the device, see parts/attention.py) the tensor-core kernels run where their conditions hold:
     portions of prompts go to the tcgen05 kernel, the rest (decoded tokens, short portions, other head
-    sizes) to the mma.sync kernels; everything else, and every step without a plan, goes to the plain kernel."""
-    if plan is None or not attention_flash_ok(q, num_q_heads, num_kv_heads, head_dim):
+    sizes) to the mma.sync kernels; everything else, and every step without a plan, goes to the plain kernel.
+    `kv_share` > 1: the plan's lists other than "big" were made for groups of num_q_heads / (num_kv_heads * kv_share)
+    query heads, kv_share of which read one cached head (see attention_flash)."""
+    if plan is None or not attention_flash_ok(q, num_q_heads, num_kv_heads * kv_share, head_dim):
         attention_plain(q, out, k_cache, v_cache, step.positions, step.token_seq, step.block_tables[group],
                         num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream)
         return
@@ -701,6 +705,6 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
         tiles = meta[kind]
         rows = min(most_rows[kind], 64)
         wide = attention_wide_clusters(head_dim) if rows <= 16 and page_size in (8, 16, 32, 64, 128) else 0
-        splits = attention_splits(tiles.shape[0], num_kv_heads, span, rows, wide_clusters=wide)
+        splits = attention_splits(tiles.shape[0], num_kv_heads * kv_share, span, rows, wide_clusters=wide)
         attention_flash(q, out, k_cache, v_cache, step.positions, step.block_tables[group], tiles, rows,
-                        num_q_heads, num_kv_heads, head_dim, page_size, window, scale, splits, stream)
+                        num_q_heads, num_kv_heads * kv_share, head_dim, page_size, window, scale, splits, stream, kv_share=kv_share)

@@ -26,7 +26,7 @@ from typing import Callable, Hashable, Optional
 import torch
 
 from .. import ops
-from .attention import TILE_ROWS, GQAttention, plan_tiles
+from .attention import DECODE_ROWS, TILE_ROWS, plan_tiles
 from .base import BatchShape, KVCacheView, KVPages, Mixer, ParamSpec, Part, Runtime, StepContext, StepPlan
 from .linear import Linear
 
@@ -79,19 +79,36 @@ class LatentAttention(Mixer):
     def cache_request(self) -> KVPages:
         return KVPages(1, self.kv_rank, 0, shared=True)
 
-    # The tile lists of the tensor-core attention kernels, as grouped-query attention makes them for a group of
-    # `heads` query heads on one key/value head.
+    # The tile lists of the tensor-core attention kernels, as grouped-query attention makes them for a group of query
+    # heads on one key/value head.  All heads read the one cached "head"; more than 16 of them are cut into `share`
+    # equal groups of at most 16 (the rows of the decode kernels' tiles), each of which reads it on its own.  The work
+    # items of the prompt kernel ("big") stay those of all heads together.
+    @property
+    def share(self) -> int:
+        if self.heads <= DECODE_ROWS:
+            return 1
+        return next((s for s in range(2, self.heads + 1) if self.heads % s == 0 and self.heads // s <= DECODE_ROWS), 1)
+
     def plan_key(self) -> Optional[Hashable]:
-        return ("attention tiles", self.heads) if self.rt.fast_kernels and self.heads <= TILE_ROWS else None
+        if not self.rt.fast_kernels or self.heads // self.share > TILE_ROWS:
+            return None
+        return ("attention tiles", self.heads, self.share)
 
     def plan(self, batch: BatchShape) -> Optional[StepPlan]:
-        if batch.max_q_len == 1:
-            key = (self.heads, len(batch.q_lens))
-            hit = GQAttention._decode_plans.get(key)
-            if hit is None:
-                hit = GQAttention._decode_plans[key] = plan_tiles(batch, self.heads)
-            return hit
-        return plan_tiles(batch, self.heads)
+        share = self.share
+        key = (self.heads, share, len(batch.q_lens)) if batch.max_q_len == 1 else None
+        if key is not None and key in self._plans_of_single_tokens:
+            return self._plans_of_single_tokens[key]
+        plan = plan_tiles(batch, self.heads // share)
+        if share > 1 and "big" in plan.arrays:
+            whole = plan_tiles(batch, self.heads)
+            plan.arrays["big"] = whole.arrays["big"]
+            plan.host["rows"]["big"] = whole.host["rows"]["big"]
+        if key is not None:
+            self._plans_of_single_tokens[key] = plan
+        return plan
+
+    _plans_of_single_tokens: dict = {}
 
     def forward(self, u: torch.Tensor, step: StepContext, cache: KVCacheView, write_cache: bool = True) -> torch.Tensor:
         rt = self.rt
@@ -111,7 +128,7 @@ class LatentAttention(Mixer):
             ops.gemm_heads(q_lat, q, self.uk_t, rt.stream)                   # the head's key map, applied to the query
         mix = rt.empty((T, H, self.kv_rank))
         ops.attention(q_lat, mix, cache.k, cache.v, step, cache.group, H, 1, self.kv_rank, cache.page_size, 0,
-                      self.scale, rt.stream, plan=step.plans.get(self.plan_key()))
+                      self.scale, rt.stream, plan=step.plans.get(self.plan_key()), kv_share=self.share)
         gated = rt.empty((T, H, self.vdim))
         ops.gemm_heads(gated, mix, self.uv, rt.stream, gate=pre[:, self.q_rank + self.kv_rank:])
         return self.o.forward(gated.view(T, H * self.vdim))

@@ -28,6 +28,8 @@ def _config(vocab, width, positions, logit_scale, eps, groups, taps, layers):
 # Q: everything that can be 1 is 1 (groups, taps, heads), one layer of each kind.
 # R: sizes at which the bfloat16 engine takes its tensor-core paths (multiples of 64 and 128), two taps.
 # S: a recurrence only (no pages at all), five taps, many small heads.
+# T: twenty heads on a latent of 64, more than a tile of the decode kernels has rows (the engine cuts them into two
+#    groups that read the one cached head), beside a recurrence with heads of 16 x 72.
 # In P and R the last attention layer has a latent so much wider than a head that the engine keeps the query's two
 # maps apart; in the other attention layers it multiplies them out.
 CONFIGS = {
@@ -37,8 +39,9 @@ CONFIGS = {
     "R": _config(331, 256, 1024, 0.125, 2e-6, 2, 2, [_hgrn2(2, 128, 64, 512), _latent(4, 64, 64, 128, 128, 0.125, 512),
                                                      _hgrn2(4, 64, 128, 256), _latent(8, 32, 48, 64, 128, 0.18, 256)]),
     "S": _config(150, 48, 400, 2.0, 1e-5, 4, 5, [_hgrn2(6, 8, 8, 96), _hgrn2(3, 12, 16, None)]),
+    "T": _config(257, 128, 600, 0.3, 1e-6, 8, 3, [_latent(20, 16, 24, 48, 64, 0.25, 192), _hgrn2(2, 16, 72, 128)]),
 }
-PAGE = {"P": 16, "Q": 8, "R": 16, "S": 16}
+PAGE = {"P": 16, "Q": 8, "R": 16, "S": 16, "T": 16}
 
 
 def make_weights(cfg: dict, seed: int, sharp: float = 1.0, keep: float | None = None) -> dict[str, torch.Tensor]:
