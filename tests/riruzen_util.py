@@ -121,3 +121,40 @@ def compare(got: dict, key, cfg: dict, weights: dict, reqs: dict[str, list[int]]
             assert err <= tol, f"request {rid}: first wrong position {p} (error {err:.3g} of scale, allowed {tol:.3g})"
             worst = max(worst, err)
     return worst
+
+
+def rounding_alone(cfg: dict, weights: dict, ids: list[int]) -> float:
+    """What rounding alone does to this model's logits: the largest change, as a fraction of the largest |logit|, when
+    the plain implementation rounds the input of every mixer and feed-forward to bfloat16 and nothing else.  Any
+    bfloat16 engine does at least that; models with tiny heads behind a norm multiply it many times."""
+    import plain_riruzen as plain
+    exact = PlainRiruzen(cfg, weights).forward(ids)
+    r = lambda x: x.to(torch.bfloat16).to(torch.float64)
+    saved = plain.hgrn2, plain.latent_attention, plain.gated_feed_forward
+    try:
+        plain.hgrn2 = lambda u, *a, **k: saved[0](r(u), *a, **k)
+        plain.latent_attention = lambda u, *a, **k: saved[1](r(u), *a, **k)
+        plain.gated_feed_forward = lambda h, *a, **k: saved[2](r(h), *a, **k)
+        rounded = PlainRiruzen(cfg, weights).forward(ids)
+    finally:
+        plain.hgrn2, plain.latent_attention, plain.gated_feed_forward = saved
+    return ((rounded - exact).abs().max() / exact.abs().max()).item()
+
+
+def random_config(seed: int) -> dict:
+    """A configuration whose every size is drawn: widths, group counts, taps, the order and number of layers, head
+    counts (above 16 too), head sizes that are no multiples of 4 or 8, layers without feed-forward."""
+    import random
+    rng = random.Random(seed)
+    groups = rng.choice([1, 2, 3, 4, 5, 6, 8])
+    width = groups * rng.choice([4, 6, 8, 10, 16, 24, 32, 40])
+    layers = []
+    for _ in range(rng.randint(1, 6)):
+        ff = rng.choice([None, 24, 64, 100, 128, 192])
+        if rng.random() < 0.5:
+            layers.append(_latent(rng.choice([1, 2, 3, 4, 6, 8, 12, 18]), rng.choice([4, 8, 10, 16, 24, 48, 64]), rng.choice([4, 8, 12, 20, 32, 80]),
+                                  rng.choice([8, 12, 32, 40, 128]), rng.choice([8, 12, 16, 24, 32, 64, 96, 128]), rng.choice([0.1, 0.125, 0.3]), ff))
+        else:
+            layers.append(_hgrn2(rng.choice([1, 2, 3, 4, 8]), rng.choice([4, 6, 16, 33, 48, 64, 100]), rng.choice([3, 8, 16, 33, 64, 70]), ff))
+    return _config(rng.choice([64, 97, 300, 577]), width, 400, rng.choice([0.5, 1.0, 3.0]), rng.choice([1e-5, 1e-6]), groups,
+                   rng.choice([1, 2, 3, 4, 6]), layers)

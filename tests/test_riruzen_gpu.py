@@ -457,6 +457,27 @@ def test_batch_against_each_alone(models, dtype):
                 assert torch.equal(together[(r, p)], alone[(r, p)]), (r, p)
 
 
+@pytest.mark.parametrize("seed", range(8))
+def test_configurations_drawn_at_random(tmp_path, seed):
+    """Every size drawn at random: the 32-bit engine must agree with the plain implementation to 32-bit rounding under
+    every cutting; the bfloat16 engine within a few times what rounding the sublayers' inputs alone does to that model."""
+    from lucciola_b200.config import EngineOptions
+    from lucciola_b200.engine.load import build_runner
+    cfg = rz.random_config(seed)
+    w = rz.make_weights(cfg, 300 + seed)
+    folder = rz.write_model(tmp_path / "model", cfg, w)
+    reqs = {f"q{i}": rz.tokens(cfg, n, salt=seed) for i, n in enumerate((1, 23, 97, 200, 64))}
+    floor = max(rz.rounding_alone(cfg, w, ids) for ids in reqs.values())
+    for dtype in DTYPES:
+        for cut in ("whole", "portions", "mixed", "tail_decoded"):
+            steps = getattr(ru, cut)(reqs)
+            pages = max(ru.max_live_tokens(steps) // 16, 1)
+            runner = build_runner(folder, EngineOptions(dtype=dtype, block_size=16, max_blocks=pages, max_num_seqs=4,
+                                                        use_cuda_graph=(cut == "mixed"), graph_after=1), num_pages=pages)
+            got = ru.replay(runner, steps, poison=True)
+            rz.compare(got, ("drawn", seed), cfg, w, reqs, dtype, tol=3e-5 if dtype == "float32" else max(rz.TOL[dtype], 4 * floor))
+
+
 # ---- through the entry point -------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype,slack", [("float32", 1e-4), ("bfloat16", 0.3)])
 @pytest.mark.parametrize("name", ["P", "R", "S"])
