@@ -9,8 +9,6 @@ x <- x + mixer(u) + ff(h).  Linear weights are [out, in].
 """
 from __future__ import annotations
 
-import math
-
 import torch
 
 
@@ -39,10 +37,6 @@ def causal_taps(h: torch.Tensor, w: torch.Tensor, history: torch.Tensor | None =
         for j in range(taps):
             out[t] += w[:, j] * ext[t + j]
     return out
-
-
-def gelu_tanh(z: torch.Tensor) -> torch.Tensor:
-    return 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
 
 
 def gated_feed_forward(h: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor) -> torch.Tensor:
