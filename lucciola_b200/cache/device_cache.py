@@ -19,7 +19,8 @@ from .manager import CacheGroup, flat_requests
 def bytes_per_page(groups: Sequence[CacheGroup], page_size: int, dtype: torch.dtype) -> int:
     """Bytes one page id costs when every group gets the same number of pages."""
     el = torch.empty((), dtype=dtype).element_size()
-    return sum(len(g.cache_ids) * (1 if g.shared else 2) * g.num_kv_heads * page_size * g.head_dim * el for g in groups)
+    return sum(len(g.cache_ids) * g.num_kv_heads * page_size * (g.head_dim + (0 if g.shared else (g.v_head_dim or g.head_dim))) * el
+               for g in groups)
 
 
 def pages_that_fit(groups: Sequence[CacheGroup], page_size: int, dtype: torch.dtype, device: torch.device,
@@ -37,7 +38,17 @@ class DeviceCache:
         self.page_size = page_size
         self.pools: list[torch.Tensor] = []
         single: dict[object, object] = {}
+        self.value_pools: dict[int, torch.Tensor] = {}      # groups whose values have another size than their keys
         for gi, g in enumerate(groups):
+            if g.v_head_dim and not g.shared:
+                # keys and values in tensors of their own: [layer][page][kv head][slot][head_dim | v_head_dim]
+                pool = torch.zeros((len(g.cache_ids), 1, num_pages[gi], g.num_kv_heads, page_size, g.head_dim), dtype=dtype, device=device)
+                vpool = torch.zeros((len(g.cache_ids), num_pages[gi], g.num_kv_heads, page_size, g.v_head_dim), dtype=dtype, device=device)
+                self.pools.append(pool)
+                self.value_pools[gi] = vpool
+                for li, key in enumerate(g.cache_ids):
+                    single[key] = KVCacheView(pool[li, 0], vpool[li], gi, page_size)
+                continue
             pool = torch.zeros((len(g.cache_ids), 1 if g.shared else 2, num_pages[gi], g.num_kv_heads, page_size, g.head_dim),
                                dtype=dtype, device=device)
             self.pools.append(pool)
@@ -68,6 +79,8 @@ class DeviceCache:
         if pages:
             idx = torch.tensor(list(pages), dtype=torch.long, device=self.pools[group].device)
             self.pools[group][:, :, idx] = value
+            if group in self.value_pools:
+                self.value_pools[group][:, idx] = value
 
     def poison_slots(self, slots: Sequence[int], value: float = float("nan")) -> None:
         """Fill the state rows of these slots with a value that would show in any sum (for tests of slot reuse)."""

@@ -31,6 +31,7 @@ class CacheGroup:
     cache_ids: tuple                 # the model's caches that live in this group: cache ids, or (cache id, place) for a
                                      # member of a cache id that asked for a tuple
     shared: bool = False             # one vector a token is key and value at once
+    v_head_dim: int = 0              # size of a value head when it differs from the keys' (0: the same)
 
 
 def flat_requests(requests: Sequence[KVPages | StateSlot | None | tuple]) -> list[tuple[object, object]]:
@@ -51,10 +52,10 @@ def plan_groups(requests: Sequence[KVPages | StateSlot | None | tuple]) -> tuple
     state_ids: list = []
     for key, r in flat_requests(requests):
         if isinstance(r, KVPages):
-            by_key.setdefault((r.num_kv_heads, r.head_dim, r.window, r.shared), []).append(key)
+            by_key.setdefault((r.num_kv_heads, r.head_dim, r.window, r.shared, r.v_head_dim if r.v_head_dim != r.head_dim else 0), []).append(key)
         elif isinstance(r, StateSlot):
             state_ids.append(key)
-    groups = [CacheGroup(k[0], k[1], k[2], tuple(v), k[3]) for k, v in by_key.items()]
+    groups = [CacheGroup(k[0], k[1], k[2], tuple(v), k[3], k[4]) for k, v in by_key.items()]
     return groups, state_ids
 
 

@@ -11,6 +11,10 @@
 // A sliding window, which lucciola does not have, adds j > pos - window.
 // Keys outside the allowed range are never read, so what a reused page still
 // holds cannot reach a sum.
+//
+// Two more things lucciola does not have.  Values may have another size than keys (v_dim; the value pool is
+// then [page][kv_head][slot][v_dim]).  And a linear distance bias: with `slopes` (one 32-bit number a query
+// head) the score of key j for the query at position i is (q . k) * scale - slopes[h] * (i - j).
 #include "common.cuh"
 
 namespace lb {
@@ -20,6 +24,8 @@ struct PlainAttnParams {
   const int* positions; const int* token_seq; const int* block_table;
   int num_q_heads, num_kv_heads, head_dim, page_size, max_pages, window;
   float scale;
+  int v_dim;               // size of a value head
+  const float* slopes;     // optional [num_q_heads]: distance bias
 };
 
 template <typename T, int DPL>
@@ -31,7 +37,8 @@ __global__ void plain_attention_kernel(PlainAttnParams p) {
   const int t = blockIdx.y;
   const int h = blockIdx.x * nwarps + warp;
   if (h >= p.num_q_heads) return;
-  const int d = p.head_dim;
+  const int d = p.head_dim, dv = p.v_dim;
+  const float slope = p.slopes ? p.slopes[h] : 0.f;
   const int kvh = h / (p.num_q_heads / p.num_kv_heads);
   float* qs = smem + (size_t)warp * d;
   const T* q = (const T*)p.q + ((size_t)t * p.num_q_heads + h) * d;
@@ -52,16 +59,16 @@ __global__ void plain_attention_kernel(PlainAttnParams p) {
   for (int base = lo; base <= pos; base += 32) {
     const int j = base + lane;
     const bool valid = j <= pos;
-    long long off = -1;
+    long long off = -1;                        // the key's place in its pool, in heads
     float s = -INFINITY;
     if (valid) {
       const int page = bt[j / p.page_size];
       if (page >= 0) {
-        off = (((long long)page * p.num_kv_heads + kvh) * p.page_size + (j % p.page_size)) * d;
-        const T* k = kc + off;
+        off = ((long long)page * p.num_kv_heads + kvh) * p.page_size + (j % p.page_size);
+        const T* k = kc + off * d;
         float acc = 0.f;
         for (int i = 0; i < d; ++i) acc += qs[i] * to_f32(k[i]);
-        s = acc * p.scale;
+        s = acc * p.scale - slope * (float)(pos - j);
       }
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -75,21 +82,21 @@ __global__ void plain_attention_kernel(PlainAttnParams p) {
       const float pv = __shfl_sync(0xffffffffu, pj, jj);
       const long long voff = __shfl_sync(0xffffffffu, off, jj);
       if (voff < 0) continue;  // uniform over the warp
-      const T* v = vc + voff;
+      const T* v = vc + voff * dv;
 #pragma unroll
       for (int i = 0; i < DPL; ++i) {
         const int dim = lane + 32 * i;
-        if (dim < d) o[i] += pv * to_f32(v[dim]);
+        if (dim < dv) o[i] += pv * to_f32(v[dim]);
       }
     }
     m = m_new;
   }
-  T* out = (T*)p.out + ((size_t)t * p.num_q_heads + h) * d;
+  T* out = (T*)p.out + ((size_t)t * p.num_q_heads + h) * dv;
   const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
   for (int i = 0; i < DPL; ++i) {
     const int dim = lane + 32 * i;
-    if (dim < d) out[dim] = from_f32<T>(o[i] * inv);
+    if (dim < dv) out[dim] = from_f32<T>(o[i] * inv);
   }
 }
 
@@ -98,7 +105,7 @@ int launch_plain(const PlainAttnParams& p, int num_tokens, cudaStream_t stream) 
   const int warps = 4;
   dim3 grid((p.num_q_heads + warps - 1) / warps, num_tokens);
   const size_t smem = (size_t)warps * p.head_dim * sizeof(float);
-  const int dpl = (p.head_dim + 31) / 32;
+  const int dpl = (p.v_dim + 31) / 32;
   if (dpl <= 1) launch(plain_attention_kernel<T, 1>, grid, dim3(warps * 32), smem, stream, p);
   else if (dpl <= 2) launch(plain_attention_kernel<T, 2>, grid, dim3(warps * 32), smem, stream, p);
   else if (dpl <= 4) launch(plain_attention_kernel<T, 4>, grid, dim3(warps * 32), smem, stream, p);
@@ -113,7 +120,9 @@ LB_EXPORT int lb_attention_plain(int dtype, const void* q, void* out, const void
                                  const void* v_cache, const int* positions, const int* token_seq,
                                  const int* block_table, int num_tokens, int num_q_heads,
                                  int num_kv_heads, int head_dim, int page_size, int max_pages,
-                                 int window, float scale, cudaStream_t stream) {
+                                 int window, float scale, int v_dim, const float* slopes, cudaStream_t stream) {
+  if (v_dim <= 0) v_dim = head_dim;
+  LB_CHECK_ARG(v_dim <= 512, "attention_plain: value size %d not in 1..512", v_dim);
   LB_CHECK_ARG(lb::valid_dtype(dtype), "attention_plain: bad dtype %d", dtype);
   LB_CHECK_ARG(head_dim > 0 && head_dim <= 512, "attention_plain: head_dim %d not in 1..512", head_dim);
   LB_CHECK_ARG(num_q_heads > 0 && num_kv_heads > 0 && num_q_heads % num_kv_heads == 0,
@@ -126,7 +135,7 @@ LB_EXPORT int lb_attention_plain(int dtype, const void* q, void* out, const void
   p.q = q; p.out = out; p.k_cache = k_cache; p.v_cache = v_cache;
   p.positions = positions; p.token_seq = token_seq; p.block_table = block_table;
   p.num_q_heads = num_q_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim;
-  p.page_size = page_size; p.max_pages = max_pages; p.window = window; p.scale = scale;
+  p.page_size = page_size; p.max_pages = max_pages; p.window = window; p.scale = scale; p.v_dim = v_dim; p.slopes = slopes;
   LB_DISPATCH_DTYPE(dtype, T, { lb::launch_plain<T>(p, num_tokens, stream); })
   LB_CHECK_LAUNCH("attention_plain");
   return 0;

@@ -6,6 +6,11 @@
 //
 // With a table of learned position vectors the row pos_table[positions[t], :] is added in 32-bit,
 // unscaled, for models that encode positions at the input instead of inside attention.
+//
+// With a table of frequencies (sin_freq, 64-bit, [ceil(hidden / 2)]) a sinusoidal position vector is added
+// instead: entry 2i gets sin(p * sin_freq[i]), entry 2i + 1 the cosine of the same angle.  The angle is formed
+// and brought into (-pi, pi] in 64-bit, so that a position in the hundreds of thousands costs no digits; sine and
+// cosine of the remainder are 32-bit.
 #include "common.cuh"
 
 namespace lb {
@@ -31,19 +36,53 @@ __global__ void embedding_kernel(float* __restrict__ out, const int* __restrict_
   }
 }
 
+template <typename TW>
+__global__ void embedding_sinusoid_kernel(float* __restrict__ out, const int* __restrict__ ids, const TW* __restrict__ table,
+                                          int hidden, int vocab, const double* __restrict__ sin_freq,
+                                          const int* __restrict__ positions) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  int id = ids[t];
+  if (id < 0 || id >= vocab) id = 0;
+  const TW* row = table + (size_t)id * hidden;
+  float* dst = out + (size_t)t * hidden;
+  const double pos = (double)positions[t];
+  const double two_pi = 6.283185307179586476925286766559;
+  for (int i = threadIdx.x; 2 * i < hidden; i += blockDim.x) {
+    const double a = pos * sin_freq[i];
+    const float r = (float)(a - two_pi * rint(a / two_pi));
+    float s, c;
+    sincosf(r, &s, &c);
+    dst[2 * i] = to_f32(row[2 * i]) + s;
+    if (2 * i + 1 < hidden) dst[2 * i + 1] = to_f32(row[2 * i + 1]) + c;
+  }
+}
+
 }  // namespace lb
 
-// pos_table (same type as table, [max_positions, hidden]) and positions are optional, together.
+// pos_table (same type as table, [max_positions, hidden]) and positions are optional, together; sin_freq
+// (with positions, without pos_table) asks for sinusoidal position vectors instead.
 LB_EXPORT int lb_embedding(float* out, const int* ids, const void* table, int table_dtype,
                            int num_tokens, int hidden, int vocab, const void* pos_table, const int* positions,
-                           int max_positions, cudaStream_t stream) {
-  LB_CHECK_ARG((pos_table == nullptr) == (positions == nullptr) && (pos_table == nullptr || max_positions > 0),
+                           int max_positions, const double* sin_freq, cudaStream_t stream) {
+  LB_CHECK_ARG(sin_freq == nullptr || (pos_table == nullptr && positions != nullptr),
+               "embedding: sinusoidal positions need the positions and exclude a table of position vectors");
+  LB_CHECK_ARG(sin_freq != nullptr || ((pos_table == nullptr) == (positions == nullptr) && (pos_table == nullptr || max_positions > 0)),
                "embedding: a position table needs positions and its number of rows");
   LB_CHECK_ARG(lb::valid_dtype(table_dtype), "embedding: bad table dtype %d", table_dtype);
   LB_CHECK_ARG(num_tokens >= 0 && hidden > 0 && vocab > 0, "embedding: bad sizes T=%d H=%d V=%d",
                num_tokens, hidden, vocab);
   if (num_tokens == 0) return 0;
   int threads = hidden >= 1024 ? 256 : (hidden >= 256 ? 128 : 64);
+  if (sin_freq) {
+    LB_DISPATCH_DTYPE(table_dtype, TW, {
+      lb::launch(lb::embedding_sinusoid_kernel<TW>, dim3(num_tokens), dim3(threads), 0, stream, out, ids, (const TW*)table, hidden,
+                 vocab, sin_freq, positions);
+    })
+    LB_CHECK_LAUNCH("embedding");
+    return 0;
+  }
   LB_DISPATCH_DTYPE(table_dtype, TW, {
     lb::launch(lb::embedding_kernel<TW>, dim3(num_tokens), dim3(threads), 0, stream, out, ids, (const TW*)table, hidden, vocab,
                (const TW*)pos_table, positions, max_positions);

@@ -1,0 +1,437 @@
+// A feed-forward of many small experts of which every token uses a few: the router's choice, the lists of tokens
+// by expert, the experts' products over those lists, and the weighted sum.
+//
+//   route      s = sigmoid(z) for the router's logits z (32-bit).  The choice is made on c = s + correction: the
+//              experts form `groups` equal groups of neighbours, a group is worth the sum of its two largest c, only
+//              the experts of the `keep` best groups can be chosen, and of those the `top` with the largest c are.
+//              Ties go to the lower index.  The weights are the chosen experts' s (without the correction), divided
+//              by their sum + 1e-20, times `scale`.
+//   dispatch   the (token, choice) pairs sorted by expert: offsets of the experts' runs, the pair at each place and
+//              the place of each pair, and the list of row tiles (expert, first place) the products walk.  One CTA;
+//              nothing comes back to the host, so a step's launches do not depend on the choices.
+//   product    y[place, :] = act(x[row(place), :] . W[e]^T) for the places of expert e, W [experts, N, K].  With
+//              `gated`, W[e] holds N/2 gate rows and then N/2 up rows and y has N/2 columns (the activations of
+//              swiglu.cu).  row(place) is the pair's token for the first product (`gather`), the place itself for the second.
+//   combine    out[t, :] = sum_k weight[t, k] * y[place(t, k), :] (+ an expert every token uses), k in the order
+//              of the choice, in 32-bit.
+//
+// Every output element is one thread's sum over k in increasing order, so a token's result does not depend on where
+// the token stands in its expert's list, nor on the batch.
+#include "common.cuh"
+
+namespace lb {
+
+// ---- route -----------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+  }
+}
+
+__global__ void route_topk_kernel(int* __restrict__ ids, float* __restrict__ weights, const float* __restrict__ logits,
+                                  long long ld, const float* __restrict__ correction, int num_tokens, int experts, int top,
+                                  int groups, int keep, float scale) {
+  extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int t = blockIdx.x * nwarps + warp;
+  if (t >= num_tokens) return;
+  float* s = smem + (size_t)warp * 3 * experts;     // plain scores
+  float* c = s + experts;                           // choice scores
+  float* gw = c + experts;                          // what a group is worth; then the sum of the chosen scores
+  const int size = experts / groups;
+  for (int e = lane; e < experts; e += 32) {
+    const float v = 1.f / (1.f + expf(-logits[(size_t)t * ld + e]));
+    s[e] = v;
+    c[e] = v + (correction ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  if (groups > 1) {
+    for (int g = lane; g < groups; g += 32) {
+      float a = -INFINITY, b = -INFINITY;           // the two largest of the group
+      for (int j = 0; j < size; ++j) {
+        const float v = c[g * size + j];
+        if (v > a) { b = a; a = v; } else if (v > b) b = v;
+      }
+      gw[g] = size > 1 ? a + b : a;
+    }
+    __syncwarp();
+    // the `keep` best groups get +inf as their mark; then every expert outside them leaves the choice
+    for (int r = 0; r < keep; ++r) {
+      float bv = -INFINITY; int bi = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32) {
+        const float v = gw[g];
+        if (v != INFINITY && (v > bv || (v == bv && g < bi))) { bv = v; bi = g; }
+      }
+      warp_argmax(bv, bi);
+      if (lane == 0 && bi < groups) gw[bi] = INFINITY;
+      __syncwarp();
+    }
+    for (int e = lane; e < experts; e += 32)
+      if (gw[e / size] != INFINITY) c[e] = -INFINITY;
+    __syncwarp();
+  }
+  float sum = 0.f;                                    // the same on every lane
+  for (int r = 0; r < top; ++r) {
+    float bv = -INFINITY; int bi = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = c[e];
+      if (!isnan(v) && (v > bv || (v == bv && e < bi))) { bv = v; bi = e; }
+    }
+    warp_argmax(bv, bi);
+    if (bi >= experts) bi = 0;                        // nothing left to choose from: cannot happen with top <= keep * size
+    sum += s[bi];
+    if (lane == 0) { ids[(size_t)t * top + r] = bi; c[bi] = NAN; }      // NaN marks a chosen expert (-inf is a legal score)
+    __syncwarp();
+  }
+  const float f = scale / (sum + 1e-20f);
+  for (int r = lane; r < top; r += 32) weights[(size_t)t * top + r] = s[ids[(size_t)t * top + r]] * f;
+}
+
+// ---- dispatch --------------------------------------------------------------------------------------------------
+// meta: [0] number of row tiles, then (expert, first place, end place) per tile from meta[4] on.
+__global__ void expert_dispatch_kernel(const int* __restrict__ ids, int pairs, int experts, int tile_rows, int* __restrict__ offsets,
+                                       int* __restrict__ pair_at, int* __restrict__ place_of, int* __restrict__ meta) {
+  extern __shared__ int ism[];
+  pdl_trigger();
+  pdl_wait();
+  int* count = ism;                 // [experts]
+  int* start = ism + experts;       // [experts + 1]
+  int* tile0 = start + experts + 1; // [experts + 1]
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+  __syncthreads();
+  // a pair's rank among its expert's pairs: whatever order the atomics give; the order never shows in a result
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) place_of[i] = atomicAdd(&count[ids[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int a = 0, tl = 0;
+    for (int e = 0; e < experts; ++e) {
+      start[e] = a; tile0[e] = tl;
+      a += count[e]; tl += (count[e] + tile_rows - 1) / tile_rows;
+    }
+    start[experts] = a; tile0[experts] = tl;
+    meta[0] = tl;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= experts; e += blockDim.x) offsets[e] = start[e];
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int place = start[ids[i]] + place_of[i];
+    place_of[i] = place;
+    pair_at[place] = i;
+  }
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) {
+    const int n = tile0[e + 1] - tile0[e];
+    for (int j = 0; j < n; ++j) {
+      int* m = meta + 4 + 3 * (tile0[e] + j);
+      m[0] = e; m[1] = start[e] + j * tile_rows; m[2] = min(start[e + 1], start[e] + (j + 1) * tile_rows);
+    }
+  }
+}
+
+// ---- product ---------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float expert_act(int act, float limit, float g, float u) {
+  if (act == 1) return fmaxf(g, 0.f) * u;
+  if (act == 2) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+  if (act == 3) {
+    g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+  }
+  return g / (1.f + expf(-g)) * u;
+}
+
+constexpr int EX_BM = 32, EX_BN = 64, EX_BK = 16;
+
+struct ExpertGemmParams {
+  void* y; const void* x; const void* w;
+  const int* meta; const int* pair_at;
+  int N, K, top;            // N: rows of W[e] (2 * columns of y when gated)
+  long long ldx, ldy;
+  int gather;               // 1: x row of a place = pair_at[place] / top; 0: the place
+  int gated, act; float limit;
+};
+
+// ordinary pipes, any types: a tile of 32 places x 64 output columns, k in increasing order by one thread an element
+template <typename TX, typename TW, typename TY, bool GATED>
+__global__ void __launch_bounds__(256) expert_gemm_plain_kernel(ExpertGemmParams p) {
+  __shared__ float xs[EX_BK][EX_BM + 4];
+  __shared__ float ws[GATED ? 2 : 1][EX_BK][EX_BN + 4];
+  __shared__ int src_row[EX_BM];
+  pdl_trigger();
+  pdl_wait();
+  if ((int)blockIdx.y >= p.meta[0]) return;
+  const int* m = p.meta + 4 + 3 * blockIdx.y;
+  const int e = m[0], r0 = m[1], r1 = m[2];
+  const int tid = threadIdx.x;
+  const int ncols = GATED ? p.N / 2 : p.N;              // output columns
+  const int n0 = blockIdx.x * EX_BN;
+  const TX* x = (const TX*)p.x;
+  const TW* w = (const TW*)p.w + (size_t)e * p.N * p.K;
+  if (tid < EX_BM) {
+    const int place = r0 + tid;
+    src_row[tid] = place < r1 ? (p.gather ? p.pair_at[place] / p.top : place) : -1;
+  }
+  __syncthreads();
+  const int tr = tid / 16, tc = tid % 16;               // rows tr * 2 .., columns tc * 4 ..
+  float acc[2][4], acc2[2][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { acc[i][j] = 0.f; acc2[i][j] = 0.f; }
+  for (int k0 = 0; k0 < p.K; k0 += EX_BK) {
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const int idx = tid + it * 256;                   // 512 = 32 rows x 16
+      const int r = idx / EX_BK, c = idx % EX_BK;
+      const int row = src_row[r], gk = k0 + c;
+      xs[c][r] = (row >= 0 && gk < p.K) ? to_f32(x[(size_t)row * p.ldx + gk]) : 0.f;
+    }
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int idx = tid + it * 256;                   // 1024 = 64 rows x 16
+      const int r = idx / EX_BK, c = idx % EX_BK;
+      const int gn = n0 + r, gk = k0 + c;
+      const bool ok = gn < ncols && gk < p.K;
+      ws[0][c][r] = ok ? to_f32(w[(size_t)gn * p.K + gk]) : 0.f;
+      if (GATED) ws[1][c][r] = ok ? to_f32(w[(size_t)(ncols + gn) * p.K + gk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < EX_BK; ++kk) {
+      float a[2], b[4], b2[4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) a[i] = xs[kk][tr * 2 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { b[j] = ws[0][kk][tc * 4 + j]; b2[j] = GATED ? ws[1][kk][tc * 4 + j] : 0.f; }
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+          if (GATED) acc2[i][j] = fmaf(a[i], b2[j], acc2[i][j]);
+        }
+    }
+    __syncthreads();
+  }
+  TY* y = (TY*)p.y;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int place = r0 + tr * 2 + i;
+    if (place >= r1) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int gn = n0 + tc * 4 + j;
+      if (gn >= ncols) continue;
+      const float v = GATED ? expert_act(p.act, p.limit, acc[i][j], acc2[i][j]) : acc[i][j];
+      y[(size_t)place * p.ldy + gn] = from_f32<TY>(v);
+    }
+  }
+}
+
+// tensor cores (mma.sync m16n8k16), bfloat16 operands, 32-bit sums: a tile of 32 places x 64 output columns a CTA of
+// four warps (warp w: rows (w & 1) * 16 .., columns (w >> 1) * 32 ..); K in blocks of 64 through shared memory.  K a
+// multiple of 8, 16-byte aligned rows.
+constexpr int EM_BM = 32, EM_BN = 64, EM_BK = 64, EM_LD = EM_BK + 8;
+
+__device__ __forceinline__ void ex_mma_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <typename TY, bool GATED>
+__global__ void __launch_bounds__(128) expert_gemm_mma_kernel(ExpertGemmParams p) {
+  __shared__ __align__(16) bf16 As[EM_BM][EM_LD];
+  __shared__ __align__(16) bf16 Bs[GATED ? 2 : 1][EM_BN][EM_LD];
+  __shared__ int src_row[EM_BM];
+  pdl_trigger();
+  pdl_wait();
+  if ((int)blockIdx.y >= p.meta[0]) return;
+  const int* m = p.meta + 4 + 3 * blockIdx.y;
+  const int e = m[0], r0 = m[1], r1 = m[2];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t4 = lane & 3;
+  const int wm = (warp & 1) * 16, wn = (warp >> 1) * 32;
+  const int ncols = GATED ? p.N / 2 : p.N;
+  const int n0 = blockIdx.x * EM_BN;
+  const bf16* x = (const bf16*)p.x;
+  const bf16* w = (const bf16*)p.w + (size_t)e * p.N * p.K;
+  if (tid < EM_BM) {
+    const int place = r0 + tid;
+    src_row[tid] = place < r1 ? (p.gather ? p.pair_at[place] / p.top : place) : -1;
+  }
+  __syncthreads();
+  float acc[4][4], acc2[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { acc[i][j] = 0.f; acc2[i][j] = 0.f; }
+  for (int k0 = 0; k0 < p.K; k0 += EM_BK) {
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const int idx = tid + it * 128;                 // 256 pieces of 8 values: 32 rows x 8
+      const int r = idx >> 3, c = (idx & 7) * 8;
+      uint4 va = make_uint4(0u, 0u, 0u, 0u);
+      const int row = src_row[r];
+      if (row >= 0 && k0 + c < p.K) va = *reinterpret_cast<const uint4*>(x + (size_t)row * p.ldx + k0 + c);
+      *reinterpret_cast<uint4*>(&As[r][c]) = va;
+    }
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+      const int idx = tid + it * 128;                 // 512 pieces: 64 rows x 8
+      const int r = idx >> 3, c = (idx & 7) * 8;
+      uint4 vb = make_uint4(0u, 0u, 0u, 0u), vb2 = vb;
+      if (n0 + r < ncols && k0 + c < p.K) {
+        vb = *reinterpret_cast<const uint4*>(w + (size_t)(n0 + r) * p.K + k0 + c);
+        if (GATED) vb2 = *reinterpret_cast<const uint4*>(w + (size_t)(ncols + n0 + r) * p.K + k0 + c);
+      }
+      *reinterpret_cast<uint4*>(&Bs[0][r][c]) = vb;
+      if (GATED) *reinterpret_cast<uint4*>(&Bs[1][r][c]) = vb2;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < EM_BK; kk += 16) {
+      uint32_t a[4];
+      const bf16* ar = &As[wm + g][kk + 2 * t4];
+      a[0] = *reinterpret_cast<const uint32_t*>(ar);
+      a[1] = *reinterpret_cast<const uint32_t*>(ar + 8 * EM_LD);
+      a[2] = *reinterpret_cast<const uint32_t*>(ar + 8);
+      a[3] = *reinterpret_cast<const uint32_t*>(ar + 8 * EM_LD + 8);
+#pragma unroll
+      for (int nb = 0; nb < 4; ++nb) {
+        uint32_t bb[2];
+        const bf16* br = &Bs[0][wn + nb * 8 + g][kk + 2 * t4];
+        bb[0] = *reinterpret_cast<const uint32_t*>(br);
+        bb[1] = *reinterpret_cast<const uint32_t*>(br + 8);
+        ex_mma_16816(acc[nb], a, bb);
+        if (GATED) {
+          const bf16* br2 = &Bs[1][wn + nb * 8 + g][kk + 2 * t4];
+          bb[0] = *reinterpret_cast<const uint32_t*>(br2);
+          bb[1] = *reinterpret_cast<const uint32_t*>(br2 + 8);
+          ex_mma_16816(acc2[nb], a, bb);
+        }
+      }
+    }
+    __syncthreads();
+  }
+  TY* y = (TY*)p.y;
+#pragma unroll
+  for (int nb = 0; nb < 4; ++nb)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int place = r0 + wm + g + 8 * half;
+      if (place >= r1) continue;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int n = n0 + wn + nb * 8 + 2 * t4 + j;
+        if (n >= ncols) continue;
+        const float v = GATED ? expert_act(p.act, p.limit, acc[nb][2 * half + j], acc2[nb][2 * half + j]) : acc[nb][2 * half + j];
+        y[(size_t)place * p.ldy + n] = from_f32<TY>(v);
+      }
+    }
+}
+
+// ---- combine ---------------------------------------------------------------------------------------------------
+template <typename TO, typename TA>
+__global__ void expert_combine_kernel(TO* __restrict__ out, const float* __restrict__ y, const float* __restrict__ weights,
+                                      const int* __restrict__ place_of, const TA* __restrict__ always, int top, int width) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  for (int j = threadIdx.x; j < width; j += blockDim.x) {
+    float acc = 0.f;
+    for (int k = 0; k < top; ++k)
+      acc = fmaf(weights[(size_t)t * top + k], y[(size_t)place_of[(size_t)t * top + k] * width + j], acc);
+    if (always) acc += to_f32(always[(size_t)t * width + j]);
+    out[(size_t)t * width + j] = from_f32<TO>(acc);
+  }
+}
+
+}  // namespace lb
+
+// ids [T, top] int32, weights [T, top] float32 from logits [T, ld] float32 and correction [experts] float32 (may be null)
+LB_EXPORT int lb_route_topk(int* ids, float* weights, const float* logits, long long ld, const float* correction,
+                            int num_tokens, int experts, int top, int groups, int keep, float scale, cudaStream_t stream) {
+  LB_CHECK_ARG(ids && weights && logits, "route_topk: null argument");
+  LB_CHECK_ARG(num_tokens >= 0 && experts > 0 && experts <= 4096 && top > 0 && top <= experts && groups > 0 && experts % groups == 0 &&
+               keep > 0 && keep <= groups && top <= keep * (experts / groups) && ld >= experts,
+               "route_topk: bad sizes experts=%d top=%d groups=%d keep=%d", experts, top, groups, keep);
+  if (num_tokens == 0) return 0;
+  const int warps = experts > 1024 ? 1 : 4;
+  const size_t smem = (size_t)warps * 3 * experts * sizeof(float);
+  lb::launch(lb::route_topk_kernel, dim3((num_tokens + warps - 1) / warps), dim3(warps * 32), smem, stream, ids, weights, logits, ld,
+             correction, num_tokens, experts, top, groups, keep, scale);
+  LB_CHECK_LAUNCH("route_topk");
+  return 0;
+}
+
+// The row tiles of the experts' products have this many places.
+LB_EXPORT int lb_expert_tile_rows() { return lb::EX_BM; }
+
+// ids [pairs] -> offsets [experts + 1], pair_at [pairs], place_of [pairs], meta [4 + 3 * (pairs / tile_rows + experts)]
+LB_EXPORT int lb_expert_dispatch(const int* ids, int pairs, int experts, int* offsets, int* pair_at, int* place_of, int* meta,
+                                 cudaStream_t stream) {
+  LB_CHECK_ARG(ids && offsets && pair_at && place_of && meta, "expert_dispatch: null argument");
+  LB_CHECK_ARG(pairs >= 0 && experts > 0 && experts <= 4096, "expert_dispatch: bad sizes pairs=%d experts=%d", pairs, experts);
+  static_assert(lb::EX_BM == lb::EM_BM, "both products walk the same row tiles");
+  const size_t smem = (size_t)(3 * experts + 2) * sizeof(int);
+  lb::launch(lb::expert_dispatch_kernel, dim3(1), dim3(1024), smem, stream, ids, pairs, experts, (int)lb::EX_BM, offsets, pair_at, place_of, meta);
+  LB_CHECK_LAUNCH("expert_dispatch");
+  return 0;
+}
+
+// y[place, :] = act(x[row(place)] . W[e]^T) over the row tiles of `meta`; max_tiles bounds their number (the grid).
+// fast: 1 allows the tensor-core kernel (bfloat16 x and W, K a multiple of 8, 16-byte aligned rows).
+LB_EXPORT int lb_expert_gemm(void* y, int y_dtype, const void* x, int x_dtype, const void* w, int w_dtype, const int* meta,
+                             const int* pair_at, int max_tiles, int N, int K, long long ldx, long long ldy, int top, int gather,
+                             int gated, int act, float limit, int fast, cudaStream_t stream) {
+  LB_CHECK_ARG(lb::valid_dtype(y_dtype) && lb::valid_dtype(x_dtype) && lb::valid_dtype(w_dtype), "expert_gemm: bad dtype");
+  LB_CHECK_ARG(y && x && w && meta && pair_at && N > 0 && K > 0 && top > 0 && max_tiles >= 0 && (!gated || N % 2 == 0) && ldx >= K,
+               "expert_gemm: bad arguments N=%d K=%d", N, K);
+  LB_CHECK_ARG(act >= 0 && act <= 3, "expert_gemm: unknown activation %d", act);
+  LB_CHECK_ARG(max_tiles <= 65535, "expert_gemm: too many row tiles (%d)", max_tiles);
+  if (max_tiles == 0) return 0;
+  lb::ExpertGemmParams p;
+  p.y = y; p.x = x; p.w = w; p.meta = meta; p.pair_at = pair_at; p.N = N; p.K = K; p.top = top; p.ldx = ldx; p.ldy = ldy;
+  p.gather = gather; p.gated = gated; p.act = act; p.limit = limit;
+  const int ncols = gated ? N / 2 : N;
+  const bool mma = fast && x_dtype == LB_BF16 && w_dtype == LB_BF16 && K % 8 == 0 && ldx % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0;
+  if (mma) {
+    dim3 grid((ncols + lb::EM_BN - 1) / lb::EM_BN, max_tiles);
+    LB_DISPATCH_DTYPE(y_dtype, TY, {
+      if (gated) lb::launch(lb::expert_gemm_mma_kernel<TY, true>, grid, dim3(128), 0, stream, p);
+      else lb::launch(lb::expert_gemm_mma_kernel<TY, false>, grid, dim3(128), 0, stream, p);
+    })
+  } else {
+    dim3 grid((ncols + lb::EX_BN - 1) / lb::EX_BN, max_tiles);
+    LB_DISPATCH_DTYPE(x_dtype, TX, {
+      LB_DISPATCH_DTYPE(w_dtype, TW, {
+        LB_DISPATCH_DTYPE(y_dtype, TY, {
+          if (gated) lb::launch(lb::expert_gemm_plain_kernel<TX, TW, TY, true>, grid, dim3(256), 0, stream, p);
+          else lb::launch(lb::expert_gemm_plain_kernel<TX, TW, TY, false>, grid, dim3(256), 0, stream, p);
+        })
+      })
+    })
+  }
+  LB_CHECK_LAUNCH("expert_gemm");
+  return 0;
+}
+
+// out[t] = sum_k weights[t, k] * y[place_of[t, k]] (+ always[t]); y float32 [pairs, width]
+LB_EXPORT int lb_expert_combine(void* out, int out_dtype, const float* y, const float* weights, const int* place_of,
+                                const void* always, int always_dtype, int num_tokens, int top, int width, cudaStream_t stream) {
+  LB_CHECK_ARG(lb::valid_dtype(out_dtype) && lb::valid_dtype(always_dtype) && out && y && weights && place_of && top > 0 && width > 0, "expert_combine: bad arguments");
+  if (num_tokens <= 0) return 0;
+  const int threads = width >= 1024 ? 256 : 128;
+  LB_DISPATCH_DTYPE(out_dtype, TO, {
+    LB_DISPATCH_DTYPE(always_dtype, TA, {
+      lb::launch(lb::expert_combine_kernel<TO, TA>, dim3(num_tokens), dim3(threads), 0, stream, (TO*)out, y, weights, place_of,
+                 (const TA*)always, top, width);
+    })
+  })
+  LB_CHECK_LAUNCH("expert_combine");
+  return 0;
+}

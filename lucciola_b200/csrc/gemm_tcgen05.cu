@@ -267,15 +267,28 @@ struct GemmParams {
                         // their partials through distributed shared memory (no workspace, no counters)
   int swiglu;           // 1, 2: the weight rows alternate in blocks of 64 between "gate" and "up" rows of the same 64
                         // features; the output has N/2 columns and holds act(gate) * up (computed in 32-bit) with
-                        // act = silu (1) or relu (2)
+                        // act = silu (1), relu (2), the tanh form of gelu (3) or the clamped swish (4, see gated_mul)
+  float act_limit = 0.f; // the clamp of activation 4
   unsigned long long wait_cycles = WAIT_CYCLES;   // after this many clock cycles a wait on a barrier gives up
   int skip_loads = 0;   // tests of the give-up path only: the producer requests nothing, so the first wait runs out
 };
 
 // silu(g) * u; the quotient by the fast division (2 ulp), the result is rounded to bfloat16 or summed with like terms afterwards
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
-// act(g) * u for the activation a gated feed-forward names: 1 silu, 2 relu
-__device__ __forceinline__ float gated_mul(int act, float g, float u) { return act == 2 ? fmaxf(g, 0.f) * u : silu_mul(g, u); }
+// act(g) * u for the activation a gated feed-forward names: 1 silu, 2 relu, 3 gelu in its tanh form,
+// 4 the clamped swish g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit)
+__device__ __forceinline__ float gated_mul(int act, float limit, float g, float u) {
+  if (act == 2) return fmaxf(g, 0.f) * u;
+  if (act == 3) {
+    const float z = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return g * (1.f - __fdividef(1.f, 1.f + __expf(2.f * z))) * u;          // 0.5 g (1 + tanh z) = g (1 - 1 / (1 + e^(2z)))
+  }
+  if (act == 4) {
+    g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit);
+    return __fdividef(g, 1.f + __expf(-1.702f * g)) * (u + 1.f);
+  }
+  return silu_mul(g, u);
+}
 
 template <int BT>
 __host__ __device__ constexpr int tmem_cols() { return BT < 32 ? 32 : BT; }
@@ -476,7 +489,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         if (feature < (p.N >> 1)) {
           for (int j = t >> 6; j < BT && m0 + j < p.M; j += 2) {
             const float rf = p.rs.on ? row_f[j] : 1.f;
-            const float v = gated_mul(p.swiglu, part_smem[j * BM + f] * rf, part_smem[j * BM + f + 64] * rf);
+            const float v = gated_mul(p.swiglu, p.act_limit, part_smem[j * BM + f] * rf, part_smem[j * BM + f + 64] * rf);
             if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)(m0 + j) * p.ldy + feature] = v;
             else ((bf16*)p.y)[(size_t)(m0 + j) * p.ldy + feature] = __float2bfloat16_rn(v);
           }
@@ -545,7 +558,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const uint32_t a = smem_base + (uint32_t)j * (BM * 4u) + (uint32_t)f * 4u;
             const float rf = p.rs.on ? row_factor(p.rs, m) : 1.f;
             const float g = cluster_sum_f32(a, splits) * rf, u = cluster_sum_f32(a + 256u, splits) * rf;
-            const float v = gated_mul(p.swiglu, g, u);
+            const float v = gated_mul(p.swiglu, p.act_limit, g, u);
             if (p.out_dtype == LB_F32) ((float*)p.y)[(size_t)m * p.ldy + feature] = v;
             else ((bf16*)p.y)[(size_t)m * p.ldy + feature] = __float2bfloat16_rn(v);
           }
@@ -1067,7 +1080,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
           if (m < p.M && feature < (p.N >> 1)) {
             float v[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = gated_mul(p.swiglu, __uint_as_float(g[j]) * rf, __uint_as_float(u[j]) * rf);
+            for (int j = 0; j < 16; ++j) v[j] = gated_mul(p.swiglu, p.act_limit, __uint_as_float(g[j]) * rf, __uint_as_float(u[j]) * rf);
             if (vec_store && feature + 16 <= (p.N >> 1)) {
               if (p.out_dtype == LB_F32) {
                 float4* dst = reinterpret_cast<float4*>((float*)p.y + (size_t)m * p.ldy + feature);
@@ -1289,7 +1302,7 @@ static int prefill_feature_tiles(const PrefillPlan& plan, int N) {
 
 static int launch_prefill(const void* y, int y_dtype, const void* x, const void* w, int M, int N, int K, long long ldx,
                           long long ldy, int swiglu, int force_bn, int pair, cudaStream_t stream,
-                          const AddNormEpilogue* an = nullptr, const RowScale* rs = nullptr) {
+                          const AddNormEpilogue* an = nullptr, const RowScale* rs = nullptr, float act_limit = 0.f) {
   bool use_pair; int m_tiles, slots; PrefillPlan plan;
   prefill_choose(M, N, K, swiglu, force_bn, pair, &use_pair, &m_tiles, &slots, &plan);
   if (use_pair && (plan.bn1 % 32 || plan.bn2 % 32)) { set_error("gemm_tcgen05: pairs of CTAs take tile widths that are multiples of 32"); return 1; }
@@ -1301,7 +1314,7 @@ static int launch_prefill(const void* y, int y_dtype, const void* x, const void*
   }
   GemmParams p;
   p.y = const_cast<void*>(y); p.workspace = nullptr; p.counters = nullptr; p.M = M; p.N = N; p.K = K; p.ldy = ldy;
-  p.out_dtype = y_dtype; p.cluster = 0; p.swiglu = swiglu;
+  p.out_dtype = y_dtype; p.cluster = 0; p.swiglu = swiglu; p.act_limit = act_limit;
   if (an) {
     p.an = *an; p.an.on = 1;
     if (p.an.tiles != prefill_feature_tiles(plan, N)) { set_error("gemm_tcgen05: %d columns of partial sums, the plan has %d feature tiles", p.an.tiles, prefill_feature_tiles(plan, N)); return 1; }
@@ -1402,7 +1415,7 @@ LB_EXPORT int lb_gemm_tcgen05_plan(int M, int N, int K, int* bt) {
 LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w, int M, int N, int K, long long ldx,
                               long long ldy, float* workspace, long long workspace_elems, int* counters,
                               int counters_len, int force_bt, int force_splits, int swiglu, const lb::RowScale* row_scale,
-                              cudaStream_t stream) {
+                              float act_limit, cudaStream_t stream) {
   LB_CHECK_ARG(!row_scale || (row_scale->sumsq && row_scale->tiles > 0), "gemm_tcgen05: a row scale without partial sums");
   LB_CHECK_ARG(lb::valid_dtype(y_dtype), "gemm_tcgen05: bad output dtype %d", y_dtype);
   LB_CHECK_ARG(M >= 0 && N > 0 && K > 0 && ldx >= K && ldy >= (swiglu ? N / 2 : N), "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
@@ -1428,7 +1441,7 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
     LB_CHECK_ARG(force_splits == 0 || (fw >= 16 && fw <= lb::PF_BN && fw % 16 == 0 && (!swiglu || fw % 128 == 0)),
                  "gemm_tcgen05: tile width %d is no multiple of 16 (128 with SwiGLU) up to 256", fw);
     LB_CHECK_ARG(force_bt >= -2, "gemm_tcgen05: token tile %d is not one of 16, 32, 64, 128, 256", force_bt);
-    if (int rc = lb::launch_prefill(y, y_dtype, x, w, M, N, K, ldx, ldy, swiglu, force_splits, -force_bt, stream, nullptr, row_scale)) return rc;
+    if (int rc = lb::launch_prefill(y, y_dtype, x, w, M, N, K, ldx, ldy, swiglu, force_splits, -force_bt, stream, nullptr, row_scale, act_limit)) return rc;
     LB_CHECK_LAUNCH("gemm_tcgen05 (many tokens)");
     return 0;
   }
@@ -1462,7 +1475,7 @@ LB_EXPORT int lb_gemm_tcgen05(void* y, int y_dtype, const void* x, const void* w
   // Clusters when the split count allows it and the caller did not ask for the workspace path
   // (force_splits < 0 asks for -force_splits splits through the workspace).
   p.cluster = (!workspace_path && splits > 1 && splits <= 8) ? splits : 0;
-  p.swiglu = swiglu;
+  p.swiglu = swiglu; p.act_limit = act_limit;
   LB_CHECK_ARG(!row_scale || splits == 1 || p.cluster > 0,
                "gemm_tcgen05: a row scale is not taken by a product that is split through the workspace (M=%d, %d splits)", M, splits);
   if (row_scale) { p.rs = *row_scale; p.rs.on = 1; }

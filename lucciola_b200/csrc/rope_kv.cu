@@ -28,16 +28,18 @@ struct RopeKvParams {
   const float* q_norm_w; const float* k_norm_w; const float* inv_freq;
   int num_q_heads, num_kv_heads, head_dim, rot_dim, page_size, max_pages;
   float eps;
+  int v_dim;                                 // size of a value head (the value pool and v_out have rows of this size)
 };
 
-template <typename T>
+// TI: the type of q_in, k_in, v_in (a product's output, which may be 32-bit where the heads are stored in bfloat16)
+template <typename T, typename TI>
 __global__ void rope_kv_kernel(RopeKvParams p) {
   extern __shared__ float smem[];
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  const int d = p.head_dim, half = p.rot_dim >> 1;
+  const int d = p.head_dim, dv = p.v_dim, half = p.rot_dim >> 1;
   float* buf = smem + (size_t)warp * d;
   const int pos = p.positions[t];
   const int total_heads = p.num_q_heads + 2 * p.num_kv_heads;
@@ -46,9 +48,10 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
   for (int h = blockIdx.y * nwarps + warp; h < total_heads; h += gridDim.y * nwarps) {
     const int kind = h < p.num_q_heads ? 0 : (h < p.num_q_heads + p.num_kv_heads ? 1 : 2);
     const int hh = kind == 0 ? h : (kind == 1 ? h - p.num_q_heads : h - p.num_q_heads - p.num_kv_heads);
-    const T* src = kind == 0 ? (const T*)p.q_in + (size_t)t * p.q_stride + (size_t)hh * d
-                 : kind == 1 ? (const T*)p.k_in + (size_t)t * p.k_stride + (size_t)hh * d
-                             : (const T*)p.v_in + (size_t)t * p.v_stride + (size_t)hh * d;
+    const int dh = kind == 2 ? dv : d;        // this head's size
+    const TI* src = kind == 0 ? (const TI*)p.q_in + (size_t)t * p.q_stride + (size_t)hh * d
+                  : kind == 1 ? (const TI*)p.k_in + (size_t)t * p.k_stride + (size_t)hh * d
+                              : (const TI*)p.v_in + (size_t)t * p.v_stride + (size_t)hh * dv;
     T* dst = nullptr;
     if (kind == 0) {
       dst = (T*)p.q_out + ((size_t)t * p.num_q_heads + hh) * d;
@@ -58,16 +61,16 @@ __global__ void rope_kv_kernel(RopeKvParams p) {
       const int slot = pos % p.page_size;
       if (page >= 0) {
         T* pool = (T*)(kind == 1 ? p.k_cache : p.v_cache);
-        dst = pool + (((size_t)page * p.num_kv_heads + hh) * p.page_size + slot) * d;
+        dst = pool + (((size_t)page * p.num_kv_heads + hh) * p.page_size + slot) * dh;
       }
     } else {
       T* o = (T*)(kind == 1 ? p.k_out : p.v_out);
-      if (o) dst = o + ((size_t)t * p.num_kv_heads + hh) * d;
+      if (o) dst = o + ((size_t)t * p.num_kv_heads + hh) * dh;
     }
     if (dst == nullptr) continue;  // uniform over the warp
 
     if (kind == 2) {
-      for (int i = lane; i < d; i += 32) dst[i] = src[i];
+      for (int i = lane; i < dv; i += 32) dst[i] = from_f32<T>(to_f32(src[i]));
       continue;
     }
     const float* w = kind == 0 ? p.q_norm_w : p.k_norm_w;
@@ -201,8 +204,10 @@ LB_EXPORT int lb_rope_kv(int dtype, const void* q_in, const void* k_in, const vo
                          const int* positions, const int* token_seq, const int* block_table,
                          const float* q_norm_w, const float* k_norm_w, const float* inv_freq,
                          int num_tokens, int num_q_heads, int num_kv_heads, int head_dim,
-                         int rot_dim, int page_size, int max_pages, float eps,
+                         int rot_dim, int page_size, int max_pages, float eps, int in_dtype, int v_dim,
                          cudaStream_t stream) {
+  if (v_dim <= 0) v_dim = head_dim;
+  LB_CHECK_ARG(lb::valid_dtype(in_dtype) && v_dim <= 1024, "rope_kv: bad input type or value size");
   LB_CHECK_ARG(lb::valid_dtype(dtype), "rope_kv: bad dtype %d", dtype);
   LB_CHECK_ARG(head_dim > 0 && head_dim <= 1024, "rope_kv: head_dim %d not in 1..1024", head_dim);
   LB_CHECK_ARG(rot_dim >= 0 && rot_dim <= head_dim && rot_dim % 2 == 0,
@@ -218,14 +223,14 @@ LB_EXPORT int lb_rope_kv(int dtype, const void* q_in, const void* k_in, const vo
   p.positions = positions; p.token_seq = token_seq; p.block_table = block_table;
   p.q_norm_w = q_norm_w; p.k_norm_w = k_norm_w; p.inv_freq = rot_dim > 0 ? inv_freq : nullptr;
   p.num_q_heads = num_q_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim;
-  p.rot_dim = rot_dim; p.page_size = page_size; p.max_pages = max_pages; p.eps = eps;
+  p.rot_dim = rot_dim; p.page_size = page_size; p.max_pages = max_pages; p.eps = eps; p.v_dim = v_dim;
   const int warps = 4;
   const size_t smem = (size_t)warps * head_dim * sizeof(float);
   // The register version: bfloat16, heads of 64 / 128 / 256, whole head rotated, every row 16-byte aligned.
   const int vec = head_dim / 32;
   const size_t word = (size_t)vec * 2;
   auto aligned = [&](const void* ptr, long long stride) { return ptr == nullptr || ((uintptr_t)ptr % word == 0 && (stride * 2) % (long long)word == 0); };
-  const bool fast = dtype == LB_BF16 && (head_dim == 64 || head_dim == 128 || head_dim == 256) &&
+  const bool fast = dtype == LB_BF16 && in_dtype == LB_BF16 && v_dim == head_dim && (head_dim == 64 || head_dim == 128 || head_dim == 256) &&
                     (p.inv_freq == nullptr || rot_dim == head_dim) && aligned(q_in, q_stride) && aligned(k_in, k_stride) &&
                     aligned(v_in, v_stride) && aligned(q_out, head_dim) && aligned(k_out, head_dim) && aligned(v_out, head_dim) &&
                     aligned(k_cache, head_dim) && aligned(v_cache, head_dim);
@@ -249,7 +254,9 @@ LB_EXPORT int lb_rope_kv(int dtype, const void* q_in, const void* k_in, const vo
     int head_blocks = (total_heads + warps - 1) / warps;
     if (head_blocks > 65535) head_blocks = 65535;
     if (head_blocks < 1) head_blocks = 1;
-    lb::launch(lb::rope_kv_kernel<T>, dim3(num_tokens, head_blocks), dim3(warps * 32), smem, stream, p);
+    LB_DISPATCH_DTYPE(in_dtype, TI, {
+      lb::launch(lb::rope_kv_kernel<T, TI>, dim3(num_tokens, head_blocks), dim3(warps * 32), smem, stream, p);
+    })
   })
   LB_CHECK_LAUNCH("rope_kv");
   return 0;

@@ -2,15 +2,27 @@
 // 32-bit and rounded once (src/kernels/swiglu.cu:8,30-36 of lucciola).  gate
 // and up are two column ranges of one matrix row (the fused gate|up product)
 // or two separate matrices; `in_stride` is the distance between their rows.
-// `act` chooses the activation of the gate: 0 silu, 1 relu (out = max(gate, 0) * up).
+// `act` chooses the activation of the gate: 0 silu, 1 relu (out = max(gate, 0) * up), 2 the tanh form of gelu,
+// 3 a clamped swish with a shifted linear part: g' = min(gate, limit), u' = clamp(up, -limit, limit),
+// out = g' * sigmoid(1.702 g') * (u' + 1).
 #include "common.cuh"
 
 namespace lb {
 
+__device__ __forceinline__ float gated_act(int act, float limit, float g, float u) {
+  if (act == 1) return fmaxf(g, 0.f) * u;
+  if (act == 2) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+  if (act == 3) {
+    g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+  }
+  return g / (1.f + expf(-g)) * u;
+}
+
 template <typename T>
 __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gate,
                               const T* __restrict__ up, long long in_stride, int inter,
-                              long long total, int act) {
+                              long long total, int act, float limit) {
   pdl_trigger();
   pdl_wait();
   for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -19,14 +31,14 @@ __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gate,
     const int c = (int)(idx - t * inter);
     const float g = to_f32(gate[t * in_stride + c]);
     const float u = to_f32(up[t * in_stride + c]);
-    out[idx] = from_f32<T>((act == 1 ? fmaxf(g, 0.f) : g / (1.f + expf(-g))) * u);
+    out[idx] = from_f32<T>(gated_act(act, limit, g, u));
   }
 }
 
 // Eight bfloat16 values a thread (16-byte accesses).
 __global__ void swiglu_bf16x8_kernel(bf16* __restrict__ out, const bf16* __restrict__ gate,
                                      const bf16* __restrict__ up, long long in_stride, int inter,
-                                     long long total8, int act) {
+                                     long long total8, int act, float limit) {
   pdl_trigger();
   pdl_wait();
   const int per_row = inter >> 3;
@@ -44,8 +56,8 @@ __global__ void swiglu_bf16x8_kernel(bf16* __restrict__ out, const bf16* __restr
     for (int i = 0; i < 4; ++i) {
       const float2 g = __bfloat1622float2(g2[i]);
       const float2 u = __bfloat1622float2(u2[i]);
-      o2[i] = act == 1 ? __floats2bfloat162_rn(fmaxf(g.x, 0.f) * u.x, fmaxf(g.y, 0.f) * u.y)
-                       : __floats2bfloat162_rn(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y);
+      o2[i] = act == 0 ? __floats2bfloat162_rn(g.x / (1.f + __expf(-g.x)) * u.x, g.y / (1.f + __expf(-g.y)) * u.y)
+                       : __floats2bfloat162_rn(gated_act(act, limit, g.x, u.x), gated_act(act, limit, g.y, u.y));
     }
     *reinterpret_cast<uint4*>(out + t * inter + c) = o4;
   }
@@ -54,10 +66,10 @@ __global__ void swiglu_bf16x8_kernel(bf16* __restrict__ out, const bf16* __restr
 }  // namespace lb
 
 LB_EXPORT int lb_swiglu(int dtype, void* out, const void* gate, const void* up, long long in_stride,
-                        int num_tokens, int inter, int act, cudaStream_t stream) {
+                        int num_tokens, int inter, int act, float limit, cudaStream_t stream) {
   LB_CHECK_ARG(lb::valid_dtype(dtype), "swiglu: bad dtype %d", dtype);
   LB_CHECK_ARG(num_tokens >= 0 && inter > 0 && in_stride >= inter, "swiglu: bad sizes");
-  LB_CHECK_ARG(act == 0 || act == 1, "swiglu: activation %d is neither silu (0) nor relu (1)", act);
+  LB_CHECK_ARG(act >= 0 && act <= 3, "swiglu: activation %d is none of silu (0), relu (1), gelu_tanh (2), clamped swish (3)", act);
   if (num_tokens == 0) return 0;
   const long long total = (long long)num_tokens * inter;
   const bool vec = dtype == LB_BF16 && inter % 8 == 0 && in_stride % 8 == 0 &&
@@ -66,12 +78,12 @@ LB_EXPORT int lb_swiglu(int dtype, void* out, const void* gate, const void* up, 
     const long long total8 = total >> 3;
     const int blocks = (int)((total8 + 255) / 256 < 148 * 16 ? (total8 + 255) / 256 : 148 * 16);
     lb::launch(lb::swiglu_bf16x8_kernel, dim3(blocks), dim3(256), 0, stream, (lb::bf16*)out, (const lb::bf16*)gate,
-               (const lb::bf16*)up, in_stride, inter, total8, act);
+               (const lb::bf16*)up, in_stride, inter, total8, act, limit);
   } else {
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     LB_DISPATCH_DTYPE(dtype, T, {
       lb::launch(lb::swiglu_kernel<T>, dim3(blocks), dim3(256), 0, stream, (T*)out, (const T*)gate, (const T*)up,
-                 in_stride, inter, total, act);
+                 in_stride, inter, total, act, limit);
     })
   }
   LB_CHECK_LAUNCH("swiglu");

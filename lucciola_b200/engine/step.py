@@ -37,7 +37,7 @@ from ..cache.device_cache import DeviceCache, pages_that_fit
 from ..cache.manager import NO_PAGE, CacheManager, plan_groups
 from ..config.engine_options import EngineOptions
 from ..models.decoder import DecoderModel
-from ..parts.base import BatchShape, PlanView, Runtime, StepContext, StepPlan
+from ..parts.base import BatchShape, Mixer, PlanView, Runtime, StepContext, StepPlan
 
 
 # Numbers of leading single tokens for which steps are recorded; a step is padded to the next one.
@@ -117,9 +117,6 @@ class ModelRunner:
         self.model, self.rt, self.options = model, rt, options
         self.device = rt.device
         self.page_size = options.block_size
-        self.max_model_len = options.max_model_len or model.max_positions
-        if self.max_model_len > model.max_positions:
-            raise ValueError(f"max_model_len {self.max_model_len} exceeds the model's {model.max_positions} positions")
         requests = model.cache_requests()
         self.groups, self.state_cache_ids = plan_groups(requests)
         if num_pages is None:
@@ -129,6 +126,12 @@ class ModelRunner:
             if num_pages <= 0:
                 raise RuntimeError("no memory left for cache pages")
         self.num_pages = int(num_pages)
+        # A model whose positions have no limit of their own (max_positions 0) takes the option, or else what all pages
+        # together hold: the block tables of a step are as wide as the longest sequence allowed.
+        positions = model.max_positions or options.max_model_len or self.num_pages * self.page_size
+        self.max_model_len = options.max_model_len or positions
+        if self.max_model_len > positions:
+            raise ValueError(f"max_model_len {self.max_model_len} exceeds the model's {positions} positions")
         self.manager = CacheManager(self.groups, self.page_size, self.num_pages, options.max_num_seqs)
         self.cache = DeviceCache(requests, self.groups, self.page_size, [self.num_pages] * len(self.groups),
                                  options.max_num_seqs, rt.act_dtype, self.device)
@@ -137,10 +140,10 @@ class ModelRunner:
         self._arange_cache = np.arange(512, dtype=np.int32)
         # The parts that plan work on the host for every step: one for each distinct key.
         self._planners: dict[Hashable, object] = {}
-        for block in model.blocks:
-            key = block.mixer.plan_key()
+        for part in [b.mixer for b in model.blocks] + [p for p in model.all_parts() if isinstance(p, Mixer)]:   # mixers may sit inside mixers
+            key = part.plan_key()
             if key is not None and key not in self._planners:
-                self._planners[key] = block.mixer
+                self._planners[key] = part
         # Steps are recorded only when every part of the model says its forward() can be.
         self._can_record = bool(options.use_cuda_graph and rt.fast_kernels and all(p.recordable for p in model.all_parts()))
         self._staging: Optional[_Staging] = None

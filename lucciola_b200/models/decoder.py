@@ -11,7 +11,7 @@ from typing import Optional, Sequence
 
 import torch
 
-from ..parts.base import Block, KVPages, Norm, Part, Runtime, StateSlot, StepContext
+from ..parts.base import Block, KVPages, Norm, Part, Runtime, StateSlot, StepContext, StreamCopy
 from ..parts.embedding import OutputHead, TokenEmbedding
 
 
@@ -73,6 +73,8 @@ class DecoderModel(Part):
             # what the call after this one offers to take over from this one's last product (see Block.entry_sink)
             nxt = self.calls[i + 1] if i + 1 < len(self.calls) else None
             block = self.blocks[c.block]
+            if isinstance(delta, StreamCopy) and not block.takes_stream_copy:
+                delta = None                             # nothing is left to be added; this block makes its own input
             next_sink = self.blocks[nxt.block].entry_sink(residual, step.num_tokens, nxt.write_cache) if nxt is not None else None
             # a block whose sublayers run side by side may leave their outputs unsummed when the norm that adds them
             # to the residual stream takes both (see Block.offers_delta_parts)
@@ -85,5 +87,7 @@ class DecoderModel(Part):
                 residual, delta = block.forward(residual, delta, step, caches[c.cache], c.write_cache)
         if logit_rows is None or logit_rows.shape[0] == 0:
             return None
+        if isinstance(delta, StreamCopy):
+            delta = None
         h = self.final_norm.add_forward(residual, delta, self.rt.act_dtype, rows=logit_rows)
         return self.head.forward(h)

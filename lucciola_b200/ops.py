@@ -30,7 +30,21 @@ def dtype_code(dt: torch.dtype) -> int:
 
 
 _SIGNATURES = {
-    "lb_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p],
+    "lb_embedding": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+    "lb_layernorm": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+    "lb_layernorm_add": [c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_float, c_float, c_void_p, c_int,
+                         c_int, c_int, c_void_p],
+    "lb_round_copy": [c_void_p, c_int, c_void_p, c_longlong, c_void_p],
+    "lb_decay_recurrence": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "lb_rmsnorm_gated": [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_float, c_float, c_int, c_int,
+                         c_void_p],
+    "lb_head_gate": [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_longlong, c_float, c_int, c_int, c_int, c_void_p],
+    "lb_route_topk": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "lb_expert_dispatch": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    "lb_expert_gemm": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong,
+                       c_longlong, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    "lb_expert_combine": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "lb_add_group_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                              c_float, c_void_p],
     "lb_scale": [c_void_p, c_longlong, c_float, c_void_p],
@@ -48,14 +62,14 @@ _SIGNATURES = {
     "lb_add_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
     "lb_rope_kv": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_longlong, c_longlong, c_void_p, c_void_p,
                    c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+                   c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
     "lb_attention_plain": [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
-    "lb_swiglu": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p],
+                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+    "lb_swiglu": [c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_float, c_void_p],
     "lb_gemm_plain": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_longlong,
                       c_longlong, c_void_p],
     "lb_gemm_tcgen05": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_void_p,
-                        c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
+                        c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p],
     "lb_gemm_tcgen05_addnorm": [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
                                 c_int, c_void_p],
     "lb_upload": [c_void_p, c_void_p, c_longlong, c_void_p],
@@ -118,16 +132,23 @@ def current_stream() -> int:
 
 
 def embedding(out: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, stream: int,
-              pos_table: torch.Tensor | None = None, positions: torch.Tensor | None = None) -> None:
-    """out[t, :] = table[ids[t], :] as float32; with a table of position vectors, + pos_table[positions[t], :]."""
+              pos_table: torch.Tensor | None = None, positions: torch.Tensor | None = None,
+              sin_freq: torch.Tensor | None = None) -> None:
+    """out[t, :] = table[ids[t], :] as float32; with a table of position vectors, + pos_table[positions[t], :]; with
+    `sin_freq` (float64 [ceil(H / 2)]) instead + the sinusoidal vector whose entries 2i, 2i + 1 are the sine and
+    cosine of positions[t] * sin_freq[i]."""
     _check(out, "embedding output", torch.float32); _check(ids, "token ids", torch.int32); _check(table, "embedding table")
     T, H = out.shape
+    if sin_freq is not None:
+        _check(sin_freq, "frequencies", torch.float64); _check(positions, "positions", torch.int32)
+        if sin_freq.shape[0] != (H + 1) // 2:
+            raise KernelError(f"{sin_freq.shape[0]} frequencies for rows of {H}")
     if pos_table is not None:
         _check(pos_table, "position table", table.dtype); _check(positions, "positions", torch.int32)
         if pos_table.shape[1] != H:
             raise KernelError(f"position vectors have {pos_table.shape[1]} values, the embedding {H}")
     _call("lb_embedding", out.data_ptr(), ids.data_ptr(), table.data_ptr(), dtype_code(table.dtype), T, H,
-          table.shape[0], _ptr(pos_table), _ptr(positions), pos_table.shape[0] if pos_table is not None else 0, stream)
+          table.shape[0], _ptr(pos_table), _ptr(positions), pos_table.shape[0] if pos_table is not None else 0, _ptr(sin_freq), stream)
 
 
 def add_group_rmsnorm(out: torch.Tensor, residual: torch.Tensor, deltas: tuple, weight: torch.Tensor, groups: int,
@@ -254,14 +275,16 @@ def rope_kv(q_in: torch.Tensor, k_in: torch.Tensor, v_in: torch.Tensor, q_out: t
             inv_freq: torch.Tensor | None = None, rot_dim: int = 0,
             k_cache: torch.Tensor | None = None, v_cache: torch.Tensor | None = None,
             token_seq: torch.Tensor | None = None, block_table: torch.Tensor | None = None, page_size: int = 0,
-            k_out: torch.Tensor | None = None, v_out: torch.Tensor | None = None) -> None:
+            k_out: torch.Tensor | None = None, v_out: torch.Tensor | None = None, v_dim: int = 0) -> None:
     """Per-head norm of q and k, rotation, and the write of k and v into pages (or into k_out, v_out).
 
-    q_in, k_in and v_in are 2-d views whose rows may be column ranges of one wider matrix."""
+    q_in, k_in and v_in are 2-d views whose rows may be column ranges of one wider matrix; they may be float32 where
+    the heads are stored in bfloat16 (a product with 32-bit output).  `v_dim`: the size of a value head if it is not
+    head_dim (the value pool then has rows of that size)."""
     T = q_in.shape[0]
-    dt = q_in.dtype
+    dt = q_out.dtype
     for t, w in ((q_in, "q"), (k_in, "k"), (v_in, "v")):
-        if not t.is_cuda or t.dtype != dt or t.stride(-1) != 1:
+        if not t.is_cuda or t.dtype != q_in.dtype or t.stride(-1) != 1:
             raise KernelError(f"{w} must be on the GPU, of one type, with unit stride in its last dimension")
     _check(q_out, "q output", dt); _check(positions, "positions", torch.int32)
     max_pages = 0
@@ -272,33 +295,39 @@ def rope_kv(q_in: torch.Tensor, k_in: torch.Tensor, v_in: torch.Tensor, q_out: t
     _call("lb_rope_kv", dtype_code(dt), q_in.data_ptr(), k_in.data_ptr(), v_in.data_ptr(), q_in.stride(0),
           k_in.stride(0), v_in.stride(0), q_out.data_ptr(), _ptr(k_out), _ptr(v_out), _ptr(k_cache), _ptr(v_cache),
           positions.data_ptr(), _ptr(token_seq), _ptr(block_table), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq),
-          T, num_q_heads, num_kv_heads, head_dim, rot_dim, page_size, max_pages, eps, stream)
+          T, num_q_heads, num_kv_heads, head_dim, rot_dim, page_size, max_pages, eps, dtype_code(q_in.dtype), v_dim, stream)
 
 
 def attention_plain(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     positions: torch.Tensor, token_seq: torch.Tensor, block_table: torch.Tensor,
                     num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
-                    stream: int) -> None:
+                    stream: int, v_dim: int = 0, slopes: torch.Tensor | None = None) -> None:
+    """`v_dim`: the size of a value head if it is not head_dim (out is then [T, heads, v_dim]); `slopes` (float32
+    [heads]): the score of key j for the query at position i is lowered by slopes[h] * (i - j)."""
     dt = q.dtype
+    if slopes is not None:
+        _check(slopes, "distance slopes", torch.float32)
     _check(q, "q"); _check(out, "attention output", dt); _check(k_cache, "k pool", dt); _check(v_cache, "v pool", dt)
     _check(positions, "positions", torch.int32); _check(token_seq, "token map", torch.int32)
     _check(block_table, "block table", torch.int32)
     _call("lb_attention_plain", dtype_code(dt), q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
           positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), q.shape[0], num_q_heads, num_kv_heads,
-          head_dim, page_size, block_table.shape[1], window, scale, stream)
+          head_dim, page_size, block_table.shape[1], window, scale, v_dim, _ptr(slopes), stream)
 
 
-GATE_ACTS = {"silu": 0, "relu": 1}
+# Activations of a gated feed-forward, out = act(gate) * up: silu, relu, the tanh form of gelu, and "clamped_swish",
+# which clamps first (g' = min(gate, limit), u' = clamp(up, -limit, limit)) and is g' * sigmoid(1.702 g') * (u' + 1).
+GATE_ACTS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "clamped_swish": 3}
 
 
-def swiglu(out: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, stream: int, act: str = "silu") -> None:
-    """out = act(gate) * up with act silu or relu; gate and up are 2-d views with the same row stride."""
+def swiglu(out: torch.Tensor, gate: torch.Tensor, up: torch.Tensor, stream: int, act: str = "silu", limit: float = 0.0) -> None:
+    """out = act(gate) * up (see GATE_ACTS); gate and up are 2-d views with the same row stride."""
     if gate.stride(0) != up.stride(0) or gate.stride(1) != 1 or up.stride(1) != 1:
         raise KernelError("gate and up need the same row stride and unit column stride")
     _check(out, "swiglu output", gate.dtype)
     T, inter = out.shape
     _call("lb_swiglu", dtype_code(out.dtype), out.data_ptr(), gate.data_ptr(), up.data_ptr(), gate.stride(0), T, inter,
-          GATE_ACTS[act], stream)
+          GATE_ACTS[act], limit, stream)
 
 
 def gemm_plain(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int) -> None:
@@ -363,12 +392,12 @@ def _row_scale(sumsq: torch.Tensor | None, width: int, eps: float):
 
 def gemm_tcgen05(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int, force_bt: int = 0,
                  force_splits: int = 0, swiglu: bool = False, sumsq: torch.Tensor | None = None, eps: float = 0.0,
-                 act: str = "silu") -> None:
+                 act: str = "silu", limit: float = 0.0) -> None:
     """y[M, N] = x[M, K] . w[N, K]^T on the tensor cores (tcgen05, accumulators in tensor memory).
 
     With `swiglu` the rows of w alternate in blocks of 64 between gate rows and up rows of the same 64
     features (see interleave_gate_up), and y[M, N/2] = act(x . gate^T) * (x . up^T), formed in the epilogue
-    (act: "silu" or "relu").
+    (act: one of GATE_ACTS; `limit` is the clamp of "clamped_swish").
     With `sumsq` [M, tiles] the rows of x lack the factor of an RMSNorm over K values: row m of the product is
     multiplied by rsqrt(sum(sumsq[m]) / K + eps), before the activation if there is one (see gemm_tcgen05_addnorm)."""
     M, K = x.shape
@@ -380,7 +409,7 @@ def gemm_tcgen05(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, stream: int,
     ws, counters = _gemm_scratch(x.device)
     _call("lb_gemm_tcgen05", y.data_ptr(), dtype_code(y.dtype), x.data_ptr(), w.data_ptr(), M, N, K,
           x.stride(0) if M > 1 else K, y.stride(0) if M > 1 else y.shape[1], ws.data_ptr(), ws.numel(), counters.data_ptr(),
-          counters.numel(), force_bt, force_splits, (1 + GATE_ACTS[act]) if swiglu else 0, _row_scale(sumsq, K, eps), stream)
+          counters.numel(), force_bt, force_splits, (1 + GATE_ACTS[act]) if swiglu else 0, _row_scale(sumsq, K, eps), limit, stream)
 
 
 class LbHeadEpilogue(ctypes.Structure):
@@ -479,6 +508,143 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     if up.shape != gate.shape or I % 64:
         raise KernelError(f"gate and up must have the same shape with a multiple of 64 rows, got {tuple(gate.shape)}, {tuple(up.shape)}")
     return torch.stack([gate.view(I // 64, 64, K), up.view(I // 64, 64, K)], dim=1).reshape(2 * I, K).contiguous()
+
+
+def layernorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float, stream: int, rows: torch.Tensor | None = None) -> None:
+    """out[i] = (x[r] - mean) / sqrt(var + eps) * weight for r = rows[i] (or i), var the mean of the squared deviations;
+    x float32."""
+    _check(out, "norm output"); _check(x, "norm input", torch.float32); _check(weight, "norm weight", torch.float32)
+    if rows is not None:
+        _check(rows, "row index", torch.int32)
+    _call("lb_layernorm", out.data_ptr(), dtype_code(out.dtype), x.data_ptr(), weight.data_ptr(), _ptr(rows), out.shape[0],
+          out.shape[-1], eps, stream)
+
+
+def layernorm_add(residual: torch.Tensor, a: torch.Tensor, b: torch.Tensor | None, sa: float, sb: float, weight: torch.Tensor,
+                  mult: float, eps: float, stream: int, copy: torch.Tensor | None = None) -> None:
+    """residual += mult * layernorm(sa * a [+ sb * b]) * weight, in 32-bit; `copy`, if given, receives the new residual
+    rounded to its type."""
+    _check(residual, "residual", torch.float32); _check(a, "sublayer output"); _check(weight, "norm weight", torch.float32)
+    if b is not None:
+        _check(b, "second sublayer output", a.dtype)
+    if a.shape != residual.shape or (b is not None and b.shape != a.shape) or (copy is not None and copy.shape != residual.shape):
+        raise KernelError("the sublayer outputs and the copy must have the residual's shape")
+    if copy is not None:
+        _check(copy, "residual copy")
+    _call("lb_layernorm_add", residual.data_ptr(), a.data_ptr(), _ptr(b), dtype_code(a.dtype), sa, sb, weight.data_ptr(), mult, eps,
+          _ptr(copy), dtype_code(copy.dtype) if copy is not None else F32, residual.shape[0], residual.shape[1], stream)
+
+
+def round_copy(out: torch.Tensor, x: torch.Tensor, stream: int) -> None:
+    """out = x (float32) rounded to out's type."""
+    _check(out, "copy"); _check(x, "source", torch.float32)
+    if out.shape != x.shape:
+        raise KernelError("a rounded copy has its source's shape")
+    _call("lb_round_copy", out.data_ptr(), dtype_code(out.dtype), x.data_ptr(), x.numel(), stream)
+
+
+def decay_recurrence(pre: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor,
+                     out: torch.Tensor, step, heads: int, dim: int, vdim: int, stream: int, max_tokens_a_seq: int = 0) -> None:
+    """Linear attention with a fixed decay per head over this step's tokens: S <- decay_h S + k v^T, out = S^T q with
+    q, k, v = silu of the columns of `pre` (float32, row-strided) at q_col, k_col, v_col; state [slots + 1, heads, dim, vdim]
+    float32 is read and written at each sequence's slot; out [T, heads * vdim] float32."""
+    _check(decay, "decay", torch.float32); _check(state, "recurrent state", torch.float32); _check(out, "recurrence output", torch.float32)
+    if pre.dtype != torch.float32 or pre.stride(1) != 1 or not pre.is_cuda:
+        raise KernelError("the input projections must be float32 on the GPU with unit column stride")
+    _call("lb_decay_recurrence", pre.data_ptr(), pre.stride(0), q_col, k_col, v_col, decay.data_ptr(), state.data_ptr(),
+          out.data_ptr(), step.cu_tokens.data_ptr(), step.state_slots.data_ptr(), step.num_seqs, heads, dim, vdim,
+          max_tokens_a_seq, stream)
+
+
+def rmsnorm_gated(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, scale: float, eps: float,
+                  stream: int) -> None:
+    """out = x * rsqrt(mean(x^2) + eps) * weight * sigmoid(gate) * scale, row by row; x float32 [T, n] contiguous, gate
+    float32 and out (any type) may be column ranges of wider matrices."""
+    _check(x, "norm input", torch.float32); _check(weight, "norm weight", torch.float32)
+    T, n = x.shape
+    if gate.dtype != torch.float32 or gate.stride(1) != 1 or out.stride(1) != 1 or tuple(gate.shape) != (T, n) or tuple(out.shape) != (T, n):
+        raise KernelError("gate (float32) and out must be [T, n] views with unit column stride")
+    _call("lb_rmsnorm_gated", out.data_ptr(), dtype_code(out.dtype), out.stride(0) if T > 1 else n, x.data_ptr(), weight.data_ptr(),
+          gate.data_ptr(), gate.stride(0) if T > 1 else n, scale, eps, T, n, stream)
+
+
+def head_gate(out: torch.Tensor, x: torch.Tensor, gate: torch.Tensor, scale: float, stream: int) -> None:
+    """out[t, h * vdim + e] = x[t, h, e] * sigmoid(gate[t, h]) * scale; x [T, heads, vdim] contiguous, gate float32 [T, heads]
+    and out [T, heads * vdim] (x's type) may be column ranges of wider matrices."""
+    _check(x, "heads")
+    T, H, vd = x.shape
+    if gate.dtype != torch.float32 or gate.stride(1) != 1 or out.stride(1) != 1 or out.dtype != x.dtype or tuple(gate.shape) != (T, H) or tuple(out.shape) != (T, H * vd):
+        raise KernelError("gate (float32 [T, heads]) and out ([T, heads * vdim], the heads' type) must have unit column stride")
+    _call("lb_head_gate", out.data_ptr(), dtype_code(out.dtype), out.stride(0) if T > 1 else H * vd, x.data_ptr(), gate.data_ptr(),
+          gate.stride(0) if T > 1 else H, scale, T, H, vd, stream)
+
+
+def route_topk(ids: torch.Tensor, weights: torch.Tensor, logits: torch.Tensor, correction: torch.Tensor | None, groups: int,
+               keep: int, scale: float, stream: int) -> None:
+    """The router's choice for every token: ids [T, top] int32 and weights [T, top] float32 from logits [T, experts]
+    float32 (row-strided).  Scores are sigmoid(logits); chosen are the `top` largest of score + correction among the
+    experts of the `keep` best of `groups` equal groups of neighbours (a group is worth its two largest); the weights
+    are the chosen plain scores over their sum (+ 1e-20), times scale."""
+    _check(ids, "expert ids", torch.int32); _check(weights, "expert weights", torch.float32)
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("the router's logits must be float32 with unit column stride")
+    if correction is not None:
+        _check(correction, "correction", torch.float32)
+    T, E = logits.shape
+    _call("lb_route_topk", ids.data_ptr(), weights.data_ptr(), logits.data_ptr(), logits.stride(0) if T > 1 else E, _ptr(correction),
+          T, E, ids.shape[1], groups, keep, scale, stream)
+
+
+def expert_tile_rows() -> int:
+    lib = library()
+    lib.lb_expert_tile_rows.restype = c_int
+    return int(lib.lb_expert_tile_rows())
+
+
+def expert_max_tiles(pairs: int, experts: int) -> int:
+    """The most row tiles the experts' products can have for this many (token, choice) pairs."""
+    return -(-pairs // expert_tile_rows()) + experts
+
+
+def expert_dispatch(ids: torch.Tensor, experts: int, offsets: torch.Tensor, pair_at: torch.Tensor, place_of: torch.Tensor,
+                    meta: torch.Tensor, stream: int) -> None:
+    """Sort the (token, choice) pairs by expert, on the device: offsets [experts + 1], pair_at [pairs] (the pair at each
+    place), place_of [pairs], meta [4 + 3 * expert_max_tiles] (the row tiles of the products)."""
+    for t, what in ((ids, "expert ids"), (offsets, "offsets"), (pair_at, "pair list"), (place_of, "places"), (meta, "tile list")):
+        _check(t, what, torch.int32)
+    pairs = ids.numel()
+    if offsets.numel() < experts + 1 or pair_at.numel() < pairs or place_of.numel() < pairs or meta.numel() < 4 + 3 * expert_max_tiles(pairs, experts):
+        raise KernelError("expert_dispatch: an output is too small")
+    _call("lb_expert_dispatch", ids.data_ptr(), pairs, experts, offsets.data_ptr(), pair_at.data_ptr(), place_of.data_ptr(),
+          meta.data_ptr(), stream)
+
+
+def expert_gemm(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, meta: torch.Tensor, pair_at: torch.Tensor, top: int,
+                gather: bool, stream: int, act: str | None = None, limit: float = 0.0, fast: bool = True) -> None:
+    """y[place] = x[row(place)] . w[e]^T for the places of every expert e (see expert_dispatch); w [experts, N, K].
+    `gather`: row(place) is the pair's token, else the place.  With `act`, w[e] is N/2 gate rows then N/2 up rows and
+    y[place] = act(gate) * up with N/2 columns."""
+    _check(y, "expert output"); _check(x, "expert input"); _check(w, "expert weights")
+    E, N, K = w.shape
+    pairs = pair_at.numel()
+    cols = N // 2 if act is not None else N
+    if x.shape[1] != K or y.shape[1] != cols or y.shape[0] != pairs:
+        raise KernelError(f"expert_gemm shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
+    _call("lb_expert_gemm", y.data_ptr(), dtype_code(y.dtype), x.data_ptr(), dtype_code(x.dtype), w.data_ptr(), dtype_code(w.dtype),
+          meta.data_ptr(), pair_at.data_ptr(), expert_max_tiles(pairs, E), N, K, K, cols, top, 1 if gather else 0,
+          1 if act is not None else 0, GATE_ACTS[act] if act is not None else 0, limit, 1 if fast else 0, stream)
+
+
+def expert_combine(out: torch.Tensor, y: torch.Tensor, weights: torch.Tensor, place_of: torch.Tensor, stream: int,
+                   always: torch.Tensor | None = None) -> None:
+    """out[t] = sum_k weights[t, k] * y[place_of[t, k]] (+ always[t]), in 32-bit, k in order."""
+    _check(out, "combined output"); _check(y, "expert outputs", torch.float32); _check(weights, "expert weights", torch.float32)
+    _check(place_of, "places", torch.int32)
+    if always is not None:
+        _check(always, "shared expert output")
+    T, W = out.shape
+    _call("lb_expert_combine", out.data_ptr(), dtype_code(out.dtype), y.data_ptr(), weights.data_ptr(), place_of.data_ptr(),
+          _ptr(always), dtype_code(always.dtype) if always is not None else F32, T, weights.shape[1], W, stream)
 
 
 def zero_rows(state: torch.Tensor, slots: torch.Tensor, stream: int) -> None:
@@ -680,16 +846,17 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
 
 def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step, group: int,
               num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
-              stream: int, plan=None, kv_share: int = 1) -> None:
+              stream: int, plan=None, kv_share: int = 1, v_dim: int = 0, slopes: torch.Tensor | None = None) -> None:
     """Causal attention of this step's queries over the pages of their requests.  With a `plan` (tile lists
     by kind on the device, see parts/attention.py) the tensor-core kernels run where their conditions hold:
     portions of prompts go to the tcgen05 kernel, the rest (decoded tokens, short portions, other head
     sizes) to the mma.sync kernels; everything else, and every step without a plan, goes to the plain kernel.
     `kv_share` > 1: the plan's lists other than "big" were made for groups of num_q_heads / (num_kv_heads * kv_share)
     query heads, kv_share of which read one cached head (see attention_flash)."""
-    if plan is None or not attention_flash_ok(q, num_q_heads, num_kv_heads * kv_share, head_dim):
+    if plan is None or (v_dim and v_dim != head_dim) or slopes is not None or not attention_flash_ok(q, num_q_heads, num_kv_heads * kv_share, head_dim):
+        # value heads of another size than the keys' and a distance bias are the plain kernel's alone
         attention_plain(q, out, k_cache, v_cache, step.positions, step.token_seq, step.block_tables[group],
-                        num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream)
+                        num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream, v_dim=v_dim, slopes=slopes)
         return
     meta, most_rows = plan.arrays, plan.host["rows"]
     longest = step.span_hint or step.max_context_len                 # a recorded step plans for a bucket of lengths

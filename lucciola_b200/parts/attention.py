@@ -75,7 +75,7 @@ class GQAttention(Mixer):
 
     def __init__(self, rt: Runtime, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position_encoding: Optional[PositionEncoding], qk_norm_eps: Optional[float], window: int = 0,
-                 scale: Optional[float] = None):
+                 scale: Optional[float] = None, names: Optional[dict] = None, v_head_dim: Optional[int] = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
         self.rt, self.prefix = rt, prefix
@@ -85,9 +85,15 @@ class GQAttention(Mixer):
         self.window = int(window)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(head_dim)
         self.q_size, self.kv_size = num_heads * head_dim, num_kv_heads * head_dim
-        self.qkv = Linear(rt, [f"{prefix}.q_proj.weight", f"{prefix}.k_proj.weight", f"{prefix}.v_proj.weight"],
-                          hidden_size, [self.q_size, self.kv_size, self.kv_size])
-        self.o = Linear(rt, f"{prefix}.o_proj.weight", self.q_size, hidden_size)
+        # tensor names: those of the Qwen3 checkpoints unless a design gives its own (keys q, k, v, o, q_norm, k_norm)
+        self.names = {"q": f"{prefix}.q_proj.weight", "k": f"{prefix}.k_proj.weight", "v": f"{prefix}.v_proj.weight",
+                      "o": f"{prefix}.o_proj.weight", "q_norm": f"{prefix}.q_norm.weight", "k_norm": f"{prefix}.k_norm.weight"}
+        self.names.update(names or {})
+        self.v_head_dim = int(v_head_dim) if v_head_dim else head_dim        # values may have another size than keys
+        self.v_size, self.out_size = num_kv_heads * self.v_head_dim, num_heads * self.v_head_dim
+        self.qkv = Linear(rt, [self.names["q"], self.names["k"], self.names["v"]],
+                          hidden_size, [self.q_size, self.kv_size, self.v_size])
+        self.o = Linear(rt, self.names["o"], self.out_size, hidden_size)
         self.q_norm_w: torch.Tensor | None = None
         self.k_norm_w: torch.Tensor | None = None
 
@@ -102,13 +108,13 @@ class GQAttention(Mixer):
     def param_specs(self) -> list[ParamSpec]:
         if self.qk_norm_eps is None:
             return []
-        return [ParamSpec(f"{self.prefix}.q_norm.weight", (self.head_dim,), "norm"),
-                ParamSpec(f"{self.prefix}.k_norm.weight", (self.head_dim,), "norm")]
+        return [ParamSpec(self.names["q_norm"], (self.head_dim,), "norm"),
+                ParamSpec(self.names["k_norm"], (self.head_dim,), "norm")]
 
     def bind(self, get: Callable[[str], torch.Tensor]) -> None:
         if self.qk_norm_eps is not None:
-            self.q_norm_w = get(f"{self.prefix}.q_norm.weight").to(torch.float32).contiguous()
-            self.k_norm_w = get(f"{self.prefix}.k_norm.weight").to(torch.float32).contiguous()
+            self.q_norm_w = get(self.names["q_norm"]).to(torch.float32).contiguous()
+            self.k_norm_w = get(self.names["k_norm"]).to(torch.float32).contiguous()
 
     def plan_key(self) -> Optional[Hashable]:
         """The tensor-core kernels run on the bfloat16 path for groups of up to 64 query heads; the tile lists
@@ -127,7 +133,7 @@ class GQAttention(Mixer):
         return plan_tiles(batch, g)
 
     def cache_request(self) -> KVPages:
-        return KVPages(self.num_kv_heads, self.head_dim, self.window)
+        return KVPages(self.num_kv_heads, self.head_dim, self.window, v_head_dim=self.v_head_dim if self.v_head_dim != self.head_dim else 0)
 
     accepts_sink = True
 
@@ -201,3 +207,77 @@ class GQAttention(Mixer):
         ops.attention(q, out, cache.k, cache.v, step, cache.group, nq, nkv, d, cache.page_size, self.window,
                       self.scale, rt.stream, plan=step.plans.get(self.plan_key()))
         return self._project_out(out.view(T, self.q_size), sink)
+
+
+def distance_slopes(num_heads: int, exponent: float = 8.0) -> list[float]:
+    """The slopes of a linear distance bias: head h gets 2^(-exponent (h + 1) / num_heads)."""
+    return [2.0 ** (-exponent * (h + 1) / num_heads) for h in range(num_heads)]
+
+
+class GatedBiasAttention(GQAttention):
+    """Grouped-query attention without rotation whose positions enter as a linear distance bias, with a sigmoid gate of
+    one number a head on the output:
+
+        score(i, j) = (q_i . k_j) * scale - slope_h * (i - j)          for the keys j the window allows
+        out_h = softmax(score) V * sigmoid(W_g x)_h                     before the output projection
+
+    Queries and keys are normed per head as in GQAttention; values may have another size than keys (`v_head_dim`).
+    q | k | v | g are one product with 32-bit output.  Beside forward(), the mixer offers the three steps apart, so that a
+    mixer that runs it beside another may stack their products: in_names() / in_sizes() (the tensors and widths of the
+    input product), inner(pre, ...) (from the product's 32-bit columns to the scaled input of the output projection,
+    written where the caller says), and `o`."""
+    accepts_sink = False
+
+    def __init__(self, rt: Runtime, prefix: str, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 v_head_dim: int, scale: float, window: int, qk_norm_eps: Optional[float], slopes: Sequence[float],
+                 names: Optional[dict] = None):
+        base = {"q": f"{prefix}.q", "k": f"{prefix}.k", "v": f"{prefix}.v", "o": f"{prefix}.o", "g": f"{prefix}.g",
+                "q_norm": f"{prefix}.q.norm", "k_norm": f"{prefix}.k.norm"}
+        base.update(names or {})
+        super().__init__(rt, prefix, hidden_size, num_heads, num_kv_heads, head_dim, None, qk_norm_eps, window, scale,
+                         names=base, v_head_dim=v_head_dim)
+        if len(slopes) != num_heads:
+            raise ValueError(f"{len(slopes)} slopes for {num_heads} heads")
+        self._slopes = [float(x) for x in slopes]
+        self.slopes: torch.Tensor | None = None
+        self.qkvg = Linear(rt, self.in_names(), hidden_size, self.in_sizes())
+        self.inner_size = self.out_size
+
+    def in_names(self) -> list[str]:
+        return [self.names["q"], self.names["k"], self.names["v"], self.names["g"]]
+
+    def in_sizes(self) -> list[int]:
+        return [self.q_size, self.kv_size, self.v_size, self.num_heads]
+
+    def children(self) -> list[Part]:
+        return [self.qkvg, self.o]
+
+    def bind(self, get: Callable[[str], torch.Tensor]) -> None:
+        super().bind(get)
+        self.slopes = torch.tensor(self._slopes, dtype=torch.float32, device=self.rt.device)
+
+    def row_scaled_ok(self, num_tokens: int, write_cache: bool = True) -> bool:
+        return False
+
+    def inner(self, pre: torch.Tensor, step: StepContext, cache: KVCacheView, out: torch.Tensor, out_scale: float,
+              write_cache: bool = True) -> None:
+        """pre: float32 [T, >= sum(in_sizes())], the columns q | k | v | g of this mixer; out: [T, inner_size] in the
+        activation type (may be a column range of a wider matrix) receives the gated heads times out_scale."""
+        rt = self.rt
+        T, nq, nkv, d, dv = pre.shape[0], self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
+        c1, c2, c3 = self.q_size, self.q_size + self.kv_size, self.q_size + self.kv_size + self.v_size
+        q = rt.empty((T, nq, d))
+        eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
+        ops.rope_kv(pre[:, :c1], pre[:, c1:c2], pre[:, c2:c3], q, step.positions, nq, nkv if write_cache else 0, d, eps, rt.stream,
+                    q_norm_w=self.q_norm_w, k_norm_w=self.k_norm_w, k_cache=cache.k, v_cache=cache.v, token_seq=step.token_seq,
+                    block_table=step.block_tables[cache.group], page_size=cache.page_size, v_dim=dv)
+        heads = rt.empty((T, nq, dv))
+        ops.attention(q, heads, cache.k, cache.v, step, cache.group, nq, nkv, d, cache.page_size, self.window, self.scale,
+                      rt.stream, plan=step.plans.get(self.plan_key()), v_dim=dv, slopes=self.slopes)
+        ops.head_gate(out, heads, pre[:, c3:c3 + nq], out_scale, rt.stream)
+
+    def forward(self, h, step: StepContext, cache: KVCacheView, write_cache: bool = True):
+        pre = self.qkvg.forward(h, out_dtype=torch.float32)
+        inner = self.rt.empty((h.shape[0], self.inner_size))
+        self.inner(pre, step, cache, inner, 1.0, write_cache)
+        return self.o.forward(inner)

@@ -49,6 +49,7 @@ class KVPages:
     head_dim: int
     window: int = 0                 # 0: all keys; W: the last W keys (the query's own included)
     shared: bool = False            # True: one vector a token serves as key and as value (a latent); half the memory
+    v_head_dim: int = 0             # size of a value head when it is not head_dim (0: the same)
 
 
 @dataclass(frozen=True)
@@ -162,6 +163,15 @@ class RowScaled:
 
 
 @dataclass
+class StreamCopy:
+    """What a block hands on as `delta` when nothing is left to be added: the residual stream is up to date, and `x` is
+    its copy rounded to the activation type.  Blocks whose sublayers read the stream itself (no norm in front) make the
+    copy in the kernel that adds a sublayer's output, so the next block of that kind need not make one; every other
+    reader takes it for None."""
+    x: torch.Tensor
+
+
+@dataclass
 class NormSink:
     """Where a part may put its output instead of returning it: added into `residual` (float32, in place), and the
     sum handed on multiplied by `weight` as RowScaled, for the norm with these weights and eps that follows."""
@@ -221,6 +231,12 @@ class Norm(Part):
                     rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
 
+    def add_normed(self, residual: torch.Tensor, outputs, scales, mult: float, copy_dtype: Optional[torch.dtype] = None):
+        """For blocks that norm a sublayer's OUTPUT: residual += mult * norm(sum_i scales[i] * outputs[i]), in 32-bit and
+        in place; returns the new residual rounded to `copy_dtype` (None: no copy).  Optional: a norm that lacks it cannot
+        sit behind a sublayer."""
+        raise NotImplementedError(f"{type(self).__name__} cannot norm a sublayer's output")
+
 
 class PositionEncoding(Part):
     def rotary_table(self) -> Optional[tuple[torch.Tensor, int]]:
@@ -275,6 +291,7 @@ class Block(Part):
     # (the outputs of sublayers that run side by side), for a norm that adds both (Norm.takes_delta_parts).
     offers_delta_parts = False
     takes_delta_parts = False       # True: forward() takes such a tuple as `delta` (its first norm adds both)
+    takes_stream_copy = False       # True: forward() takes a StreamCopy as `delta` (see there)
 
     def cache_request(self) -> KVPages | StateSlot | None | tuple:
         """What a call of this block keeps of past tokens: the mixer's cache, unless the block has state of its own

@@ -10,7 +10,7 @@ from typing import Optional
 import torch
 
 from .. import ops
-from .base import Block, FeedForward, Mixer, Norm, NormSink, Part, RowScaled, StepContext
+from .base import Block, FeedForward, Mixer, Norm, NormSink, Part, RowScaled, StepContext, StreamCopy
 from .causal_taps import CausalTaps
 
 
@@ -95,3 +95,45 @@ class ParallelBlock(Block):
         # the norm that follows adds one delta only: the mixer's output goes into the residual stream here
         ops.add_into(residual, a, self._rt.stream)
         return residual, b
+
+
+class PostNormBlock(Block):
+    """Norm on the sublayer's output only: r += m * norm1(mixer(r)); r += m * norm2(ffn(r)).  The sublayers read the
+    residual stream itself; `m` is one multiplier for both.  A block may have no feed-forward.
+
+    The stream is 32-bit; what the sublayers' products read is its copy in the activation type, which the kernel that
+    adds a normed output writes in the same pass (Norm.add_normed) and which the block hands on as StreamCopy, so only
+    the first block of a model makes a copy by a kernel of its own.  In a 32-bit engine the sublayers read the stream
+    directly."""
+    recordable = True
+    takes_stream_copy = True
+
+    def __init__(self, mixer: Mixer, feed_forward: Optional[FeedForward], mixer_norm: Norm, ffn_norm: Optional[Norm],
+                 residual_mult: float, act_dtype: torch.dtype):
+        if (feed_forward is None) != (ffn_norm is None):
+            raise ValueError("a feed-forward and its norm come together")
+        self.mixer, self.feed_forward, self.mixer_norm, self.ffn_norm = mixer, feed_forward, mixer_norm, ffn_norm
+        self.residual_mult, self.act_dtype = float(residual_mult), act_dtype
+        self._rt = mixer_norm.rt
+
+    def children(self) -> list[Part]:
+        return [p for p in (self.mixer, self.mixer_norm, self.feed_forward, self.ffn_norm) if p is not None]
+
+    def forward(self, residual: torch.Tensor, delta, step: StepContext, cache, write_cache: bool = True):
+        exact = self.act_dtype == torch.float32
+        copy_dtype = None if exact else self.act_dtype
+        if isinstance(delta, StreamCopy):
+            h = delta.x
+        else:
+            if delta is not None:                       # a block of another kind left something to be added
+                ops.add_into(residual, delta, self._rt.stream)
+            h = residual
+            if not exact:
+                h = self._rt.empty(residual.shape)
+                ops.round_copy(h, residual, self._rt.stream)
+        a = self.mixer.forward(h, step, cache, write_cache)
+        h = self.mixer_norm.add_normed(residual, (a,), (1.0,), self.residual_mult, copy_dtype)
+        if self.feed_forward is not None:
+            b = self.feed_forward.forward(residual if exact else h, step)
+            h = self.ffn_norm.add_normed(residual, (b,), (1.0,), self.residual_mult, copy_dtype)
+        return residual, (None if exact else StreamCopy(h))

@@ -1,0 +1,83 @@
+"""Linear attention with a fixed decay per head ("lightning attention").  Per head, with a state S [dim, vdim]:
+
+    q = silu(W_q x)    k = silu(W_k x)    v = silu(W_v x)
+    S_t = decay_h S_(t-1) + k_t v_t^T        o_t = S_t^T q_t
+    out = W_o ( rmsnorm(concat_h o_t) * w * sigmoid(W_g x) )       (one norm over all heads, w [heads * vdim])
+
+The state is 32-bit, one slot a request, zero for a new request, and is all this mixer keeps of the past: prompts,
+portions and decoded tokens go through the same kernel, which walks a sequence's tokens of the step in order from the
+state the step before left.  W_q | W_k | W_v | W_g are one product with 32-bit output; the activations, the recurrence,
+the norm and the gate are computed in 32-bit.
+
+Beside forward(), the mixer offers its three steps apart (in_names / in_sizes, inner, `o`), so that a mixer that runs
+it beside another may stack their products (see SideBySideMixer).
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional, Sequence
+
+import torch
+
+from .. import ops
+from .base import Mixer, ParamSpec, Part, Runtime, StateCacheView, StateSlot, StepContext
+from .linear import Linear
+
+
+class DecayLinearAttention(Mixer):
+    recordable = True
+
+    def __init__(self, rt: Runtime, prefix: str, width: int, heads: int, dim: int, vdim: int, decay: Sequence[float], eps: float,
+                 names: Optional[dict] = None):
+        if len(decay) != heads:
+            raise ValueError(f"{len(decay)} decays for {heads} heads")
+        self.rt, self.prefix = rt, prefix
+        self.width, self.heads, self.dim, self.vdim, self.eps = width, heads, dim, vdim, float(eps)
+        self.names = {"q": f"{prefix}.q", "k": f"{prefix}.k", "v": f"{prefix}.v", "g": f"{prefix}.g", "o": f"{prefix}.o",
+                      "norm": f"{prefix}.norm"}
+        self.names.update(names or {})
+        self._decay = [float(x) for x in decay]
+        self.inner_size = heads * vdim
+        self.qkvg = Linear(rt, self.in_names(), width, self.in_sizes())
+        self.o = Linear(rt, self.names["o"], self.inner_size, width)
+        self.decay: torch.Tensor | None = None
+        self.norm_w: torch.Tensor | None = None
+
+    def in_names(self) -> list[str]:
+        return [self.names["q"], self.names["k"], self.names["v"], self.names["g"]]
+
+    def in_sizes(self) -> list[int]:
+        n = self.heads * self.dim
+        return [n, n, self.inner_size, self.inner_size]
+
+    def children(self) -> list[Part]:
+        return [self.qkvg, self.o]
+
+    def param_specs(self) -> list[ParamSpec]:
+        return [ParamSpec(self.names["norm"], (self.inner_size,), "norm")]
+
+    def bind(self, get: Callable[[str], torch.Tensor]) -> None:
+        self.norm_w = get(self.names["norm"]).to(torch.float32).contiguous()
+        self.decay = torch.tensor(self._decay, dtype=torch.float32, device=self.rt.device)
+
+    def cache_request(self) -> StateSlot:
+        return StateSlot((self.heads, self.dim, self.vdim), torch.float32)
+
+    def inner(self, pre: torch.Tensor, step: StepContext, cache: StateCacheView, out: torch.Tensor, out_scale: float,
+              write_cache: bool = True) -> None:
+        """pre: float32 [T, >= sum(in_sizes())], the columns q | k | v | g of this mixer; out: [T, inner_size] in the
+        activation type (may be a column range of a wider matrix) receives the normed, gated heads times out_scale."""
+        if not write_cache:
+            raise ops.KernelError("a recurrent mixer has no cache another call could have written")
+        rt, n = self.rt, self.heads * self.dim
+        T = pre.shape[0]
+        o = rt.empty((T, self.inner_size), torch.float32)
+        ops.decay_recurrence(pre, 0, n, 2 * n, self.decay, cache.state, o, step, self.heads, self.dim, self.vdim, rt.stream,
+                             max_tokens_a_seq=step.max_q_len)
+        g0 = 2 * n + self.inner_size
+        ops.rmsnorm_gated(out, o, self.norm_w, pre[:, g0:g0 + self.inner_size], out_scale, self.eps, rt.stream)
+
+    def forward(self, h: torch.Tensor, step: StepContext, cache: StateCacheView, write_cache: bool = True) -> torch.Tensor:
+        pre = self.qkvg.forward(h, out_dtype=torch.float32)
+        inner = self.rt.empty((h.shape[0], self.inner_size))
+        self.inner(pre, step, cache, inner, 1.0, write_cache)
+        return self.o.forward(inner)

@@ -13,21 +13,27 @@ from .linear import Linear
 class TokenEmbedding(Part):
     """residual[t, :] = table[id_t, :], unscaled (src/kernels/embedding.cu:22-38 of lucciola), as float32.
     With `positions_name` the model has a table of learned position vectors [max_positions, hidden], and
-    residual[t, :] += positions[p_t, :] (unscaled, added in 32-bit); forward() then takes the tokens' positions."""
+    residual[t, :] += positions[p_t, :] (unscaled, added in 32-bit); forward() then takes the tokens' positions.
+    With `sinusoid_base` b a sinusoidal vector is added instead, for positions without a limit: entry 2i is
+    sin(p * b^(-2i / hidden)), entry 2i + 1 the cosine of the same angle; the frequencies are made once in 64-bit."""
     recordable = True
 
     def __init__(self, rt: Runtime, name: str, vocab_size: int, hidden_size: int, positions_name: str | None = None,
-                 max_positions: int = 0):
+                 max_positions: int = 0, sinusoid_base: float | None = None):
         self.rt, self.name, self.vocab_size, self.hidden_size = rt, name, vocab_size, hidden_size
         self.positions_name, self.max_positions = positions_name, max_positions
         if positions_name is not None and max_positions <= 0:
             raise ValueError("a table of position vectors needs its number of rows")
+        if positions_name is not None and sinusoid_base is not None:
+            raise ValueError("positions are a table of vectors or sinusoids, not both")
+        self.sinusoid_base = float(sinusoid_base) if sinusoid_base is not None else None
         self.weight: torch.Tensor | None = None
         self.position_table: torch.Tensor | None = None
+        self.sin_freq: torch.Tensor | None = None
 
     @property
     def uses_positions(self) -> bool:
-        return self.positions_name is not None
+        return self.positions_name is not None or self.sinusoid_base is not None
 
     def param_specs(self) -> list[ParamSpec]:
         specs = [ParamSpec(self.name, (self.vocab_size, self.hidden_size), "embedding")]
@@ -39,12 +45,17 @@ class TokenEmbedding(Part):
         self.weight = get(self.name).contiguous()
         if self.positions_name is not None:
             self.position_table = get(self.positions_name).to(self.weight.dtype).contiguous()
+        if self.sinusoid_base is not None:
+            i = torch.arange((self.hidden_size + 1) // 2, dtype=torch.float64)
+            self.sin_freq = (self.sinusoid_base ** (-2.0 * i / self.hidden_size)).to(self.weight.device).contiguous()
 
     def forward(self, token_ids: torch.Tensor, positions: torch.Tensor | None = None) -> torch.Tensor:
         out = self.rt.empty((token_ids.shape[0], self.hidden_size), torch.float32)
-        if self.positions_name is not None:
-            if positions is None:
-                raise ValueError("this embedding adds position vectors and needs the tokens' positions")
+        if self.uses_positions and positions is None:
+            raise ValueError("this embedding adds position vectors and needs the tokens' positions")
+        if self.sinusoid_base is not None:
+            ops.embedding(out, token_ids, self.weight, self.rt.stream, positions=positions, sin_freq=self.sin_freq)
+        elif self.positions_name is not None:
             ops.embedding(out, token_ids, self.weight, self.rt.stream, pos_table=self.position_table, positions=positions)
         else:
             ops.embedding(out, token_ids, self.weight, self.rt.stream)

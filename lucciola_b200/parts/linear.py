@@ -3,6 +3,10 @@
 A Linear may be made of several checkpoint tensors stacked along the output
 dimension (q|k|v, gate|up): one product instead of several.  lucciola keeps
 them apart and runs one product each (src/qwen.cc:592-615, 762-777).
+
+With `in_features` a list, the tensors are stacked along the INPUT dimension instead ([out, in_0 | in_1 | ...]):
+the sum of several maps of several inputs as one product over the inputs laid side by side (the output
+projections of mixers that run side by side).
 """
 from __future__ import annotations
 
@@ -17,10 +21,20 @@ from .base import NormSink, ParamSpec, Part, RowScaled, Runtime
 class Linear(Part):
     recordable = True
 
-    def __init__(self, rt: Runtime, names: str | Sequence[str], in_features: int, out_features: int | Sequence[int],
+    def __init__(self, rt: Runtime, names: str | Sequence[str], in_features: int | Sequence[int], out_features: int | Sequence[int],
                  init: str = "linear"):
         self.rt = rt
         self.names = [names] if isinstance(names, str) else list(names)
+        self.in_sizes = None if isinstance(in_features, int) else list(in_features)
+        if self.in_sizes is not None:
+            if not isinstance(out_features, int) or len(self.in_sizes) != len(self.names):
+                raise ValueError("tensors stacked along the input share one output size and have an input size each")
+            self.out_sizes = [out_features]
+            self.in_features = sum(self.in_sizes)
+            self.out_features = out_features
+            self.init = init
+            self.weight = None
+            return
         self.out_sizes = [out_features] if isinstance(out_features, int) else list(out_features)
         if len(self.names) != len(self.out_sizes):
             raise ValueError("one output size for each tensor name")
@@ -30,6 +44,8 @@ class Linear(Part):
         self.weight: torch.Tensor | None = None
 
     def param_specs(self) -> list[ParamSpec]:
+        if self.in_sizes is not None:
+            return [ParamSpec(n, (self.out_features, i), self.init) for n, i in zip(self.names, self.in_sizes)]
         return [ParamSpec(n, (o, self.in_features), self.init) for n, o in zip(self.names, self.out_sizes)]
 
     def bind(self, get: Callable[[str], torch.Tensor]) -> None:
@@ -40,7 +56,7 @@ class Linear(Part):
             dt = ws[0].dtype
             if any(w.dtype != dt for w in ws):
                 raise ValueError(f"tensors {self.names} are stacked into one product and must share a type")
-            self.weight = torch.cat(ws, dim=0).contiguous()
+            self.weight = torch.cat(ws, dim=1 if self.in_sizes is not None else 0).contiguous()
 
     def bind_tensor(self, weight: torch.Tensor) -> None:
         """Use a tensor another part owns (a tied output head)."""

@@ -1,5 +1,5 @@
 """Dense gated feed-forward: down( act(gate(h)) * up(h) ), act = silu (src/qwen.cc:762-794,
-src/kernels/swiglu.cu:30-36 of lucciola) or relu.  gate and up are one product over the stacked weights; on
+src/kernels/swiglu.cu:30-36 of lucciola), relu, the tanh form of gelu, or a clamped swish with its limit (ops.GATE_ACTS).  gate and up are one product over the stacked weights; on
 the bfloat16 path, when the intermediate size is a multiple of 64, their rows are interleaved in blocks of 64
 and act(gate) * up is formed in that product's epilogue, so the [T, 2 * intermediate] matrix is never written.
 
@@ -20,10 +20,11 @@ class GatedFeedForward(FeedForward):
     recordable = True
 
     def __init__(self, rt: Runtime, gate_name: str, up_name: str, down_name: str, hidden_size: int, intermediate_size: int,
-                 act: str = "silu"):
+                 act: str = "silu", limit: float = 0.0, out_dtype: Optional[torch.dtype] = None):
         if act not in ops.GATE_ACTS:
             raise ValueError(f"activation {act!r} of a gated feed-forward is not one of {sorted(ops.GATE_ACTS)}")
-        self.rt, self.act = rt, act
+        self.rt, self.act, self.limit = rt, act, float(limit)
+        self.out_dtype = out_dtype          # type of the down product's output (None: the activation type)
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.gate_up = Linear(rt, [gate_name, up_name], hidden_size, [intermediate_size, intermediate_size])
         self.down = Linear(rt, down_name, intermediate_size, hidden_size)
@@ -48,9 +49,9 @@ class GatedFeedForward(FeedForward):
         return self.fused
 
     def _down(self, act: torch.Tensor, sink: Optional[NormSink]):
-        if sink is not None and self.down.sink_ok(act):
+        if sink is not None and self.out_dtype is None and self.down.sink_ok(act):
             return self.down.forward_into(act, sink)
-        return self.down.forward(act)
+        return self.down.forward(act, out_dtype=self.out_dtype)
 
     def forward(self, h, step: StepContext, sink: Optional[NormSink] = None):
         inter = self.intermediate_size
@@ -58,17 +59,17 @@ class GatedFeedForward(FeedForward):
             if not self.row_scaled_ok(h.shape[0]):
                 raise ops.KernelError("this feed-forward was handed rows without their norm factor for a step it cannot take them in")
             act = self.rt.empty((h.shape[0], inter))
-            ops.gemm_tcgen05(act, h.x, self.gate_up.weight, self.rt.stream, swiglu=True, sumsq=h.sumsq, eps=h.eps, act=self.act)
+            ops.gemm_tcgen05(act, h.x, self.gate_up.weight, self.rt.stream, swiglu=True, sumsq=h.sumsq, eps=h.eps, act=self.act, limit=self.limit)
             return self._down(act, sink)
         if self.fused and ops.gemm_tcgen05_ok(h, h, self.gate_up.weight):
             act = self.rt.empty((h.shape[0], inter))
-            ops.gemm_tcgen05(act, h, self.gate_up.weight, self.rt.stream, swiglu=True, act=self.act)
+            ops.gemm_tcgen05(act, h, self.gate_up.weight, self.rt.stream, swiglu=True, act=self.act, limit=self.limit)
             return self._down(act, sink)
         if self.fused:
             raise ops.KernelError("the interleaved gate|up weights need the tensor-core product (bfloat16, 16-byte aligned input)")
         gu = self.gate_up.forward(h)
         act = self.rt.empty((h.shape[0], inter))
-        ops.swiglu(act, gu[:, :inter], gu[:, inter:], self.rt.stream, act=self.act)
+        ops.swiglu(act, gu[:, :inter], gu[:, inter:], self.rt.stream, act=self.act, limit=self.limit)
         return self._down(act, sink)
 
 
