@@ -28,6 +28,8 @@ decode step of the whole batch.  The line printed at the end is one JSON object:
 `--design riruzen` measures another workload instead and leaves the default one alone: prefill and decode throughput of the
 Riruzen design (parallel blocks, alternating HGRN2 and latent-attention mixers) at layer sizes of real models, beside the Qwen3
 decoder of this engine at the same width, feed-forward size, head count and depth; one JSON line a (size, model), random weights.
+`--design bonolorn` does the same for the Bonolorn design (blocks that norm a sublayer's output; windowed attention with a distance
+bias beside decay linear attention; gelu feed-forwards and routed experts in turn), beside Qwen3 and Riruzen at equal sizes.
 
 Peaks come from MEASURED_PEAKS.json beside this file when the driver wrote it, else from the
 fallback figures 6650 GB/s and 1590 TFLOP/s.  The timed work reads far more than the 126 MB of L2
@@ -444,11 +446,53 @@ def design_configs(size: dict, layers: int, positions: int) -> dict:
                "norm": {"eps": 1e-6, "groups": 4}, "canon": {"taps": 4}, "layers": [rec if i % 2 == 0 else att for i in range(layers)]}
     qwen3 = dict(QWEN3_8B, num_hidden_layers=layers, hidden_size=W, num_attention_heads=H, num_key_value_heads=max(H // 4, 1), head_dim=D,
                  intermediate_size=size["ff"], vocab_size=size["vocab"], max_position_embeddings=positions, tie_word_embeddings=True)
-    return {"riruzen": riruzen, "qwen3": qwen3}
+    # Bonolorn: half the heads attend (grouped keys, a window of 1024), half run the decay recurrence; layers take a gelu
+    # feed-forward and 16 routed experts (4 a token, an eighth of the feed-forward each, one of a quarter for every token) in turn
+    left = {"heads": H // 2, "kv_heads": max(H // 8, 1), "dim": D, "vdim": D, "scale": D ** -0.5, "mask": {"size": 1024}}
+    right = {"heads": H // 2, "dim": D, "vdim": D, "decay": [1.0 - 2.0 ** -(3 + 8 * h / max(H // 2 - 1, 1)) for h in range(H // 2)]}
+    mixer = {"left": left, "left_scale": 0.6, "right": right, "right_scale": 0.9}
+    moe = {"kind": "moe", "expert": {"ff": size["ff"] // 8, "limit": 7.0},
+           "router": {"experts": 16, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}}, "shared": {"ff": size["ff"] // 4, "limit": 7.0}}
+    bonolorn = {"architecture": "Bonolorn", "vocab": size["vocab"], "width": W, "residual_mult": 0.3, "norm": {"eps": 1e-5},
+                "layers": [{"type": "parallel", "mixer": mixer, "mlp": {"kind": "dense", "ff": size["ff"]} if i % 2 == 0 else moe}
+                           for i in range(layers)]}
+    return {"riruzen": riruzen, "qwen3": qwen3, "bonolorn": bonolorn}
+
+
+def bonolorn_costs(cfg: dict) -> dict:
+    """The same for a Bonolorn configuration.  A decode step of B tokens reads at most B * top experts of a layer, which the
+    caller adds (`expert_bytes`, `experts`, `top`); the window bounds the keys and values a step reads (`window`)."""
+    W = cfg["width"]
+    weights = active = token_bytes = request_bytes = 0
+    attn, expert_layers = [], []
+    window = 0
+    for l in cfg["layers"]:
+        a, r = l["mixer"]["left"], l["mixer"]["right"]
+        n = (a["heads"] * a["dim"] + a["kv_heads"] * (a["dim"] + a["vdim"]) + a["heads"]) * W + W * a["heads"] * a["vdim"]
+        n += (2 * r["heads"] * r["dim"] + 2 * r["heads"] * r["vdim"]) * W + W * r["heads"] * r["vdim"]
+        token_bytes += 2 * a["kv_heads"] * (a["dim"] + a["vdim"])
+        window = a.get("mask", {}).get("size", 0)
+        request_bytes += 2 * 4 * r["heads"] * r["dim"] * r["vdim"]
+        attn.append(lambda T, a=a, r=r: a["heads"] * 2.0 * (a["dim"] + a["vdim"]) * sum(min(t + 1, a.get("mask", {}).get("size", 0) or t + 1) for t in range(T))
+                    + 6.0 * T * r["heads"] * r["dim"] * r["vdim"])
+        m = l["mlp"]
+        if m and m["kind"] == "dense":
+            n += 3 * m["ff"] * W
+        elif m:
+            one = 3 * m["expert"]["ff"] * W
+            n += m["router"]["experts"] * W + (3 * m["shared"]["ff"] * W if m.get("shared") else 0)
+            expert_layers.append((one, m["router"]["experts"], m["router"]["top"]))
+            active += m["router"]["top"] * one
+        weights += n
+    return {"weight_bytes": 2 * (weights + cfg["vocab"] * W), "token_bytes": token_bytes, "request_bytes": request_bytes,
+            "flops_per_token": 2.0 * (weights + active), "attn_flops": lambda T: sum(f(T) for f in attn), "window": window,
+            "expert_layers": expert_layers}
 
 
 def design_costs(name: str, cfg: dict) -> dict:
     """Weights a decode step reads, cache bytes a cached token and a live request cost a step, FLOPs of the products a token."""
+    if name == "bonolorn":
+        return bonolorn_costs(cfg)
     if name == "qwen3":
         L = cfg["num_hidden_layers"]
         per_layer, weight_bytes, kv = model_bytes_and_flops(cfg, L)
@@ -499,6 +543,8 @@ def run_design(args) -> int:
     for sname in sizes:
         for mname, cfg in design_configs(DESIGN_SIZES[sname], layers, max(ctx, T) + K + Wm + 64).items():
             if args.design_models and mname not in args.design_models.split(","):
+                continue
+            if mname == "bonolorn" and args.design != "bonolorn":
                 continue
             cost = design_costs(mname, cfg)
             V = cfg.get("vocab", cfg.get("vocab_size"))
@@ -557,7 +603,9 @@ def run_design(args) -> int:
                 steps = 1 if args.profile else K
                 ms = a.elapsed_time(b) / steps
                 mean_ctx = sum(runner.length(r) for r in rids) / B - steps / 2
-                step_bytes = cost["weight_bytes"] + B * (mean_ctx * cost["token_bytes"] + cost["request_bytes"])
+                seen = min(mean_ctx, cost["window"]) if cost.get("window") else mean_ctx          # a window bounds the keys a step reads
+                step_bytes = cost["weight_bytes"] + B * (seen * cost["token_bytes"] + cost["request_bytes"])
+                step_bytes += sum(2 * one * min(E, B * top) for one, E, top in cost.get("expert_layers", ()))
                 out[f"decode_b{B}"] = {"context": int(mean_ctx), "ms_per_step": round(ms, 4), "tokens_per_s": round(B / ms * 1e3, 1),
                                        "launches_per_step": (runner.kernel_launches() - launches0) // steps,
                                        "frac_of_hbm_peak": round(step_bytes / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)}
@@ -602,12 +650,12 @@ def main() -> int:
     ap.add_argument("--portion", type=int, default=512, help="tokens of the portion of a --profile mixed step")
     ap.add_argument("--time-kernel", choices=["attention_key_ranges"], default=None,
                     help="time one kernel alone over a grid of sizes, print a line of JSON a case, and exit")
-    ap.add_argument("--design", choices=["riruzen"], default=None,
+    ap.add_argument("--design", choices=["riruzen", "bonolorn"], default=None,
                     help="instead of the default workload: prefill and decode of this design beside the Qwen3 decoder at equal "
                          "sizes (--design-sizes; --layers, default 8; --prefill-tokens; --context up to 2048; --profile decode|prefill "
                          "with --batch runs one step between cudaProfilerStart/Stop)")
     ap.add_argument("--design-sizes", default="w2048,w4096", help="which of %s" % ", ".join(sorted(DESIGN_SIZES)))
-    ap.add_argument("--design-models", default="", help="riruzen, qwen3 or both (empty)")
+    ap.add_argument("--design-models", default="", help="which of riruzen, qwen3, bonolorn (empty: the design and those beside it)")
     args = ap.parse_args()
     if args.time_kernel == "attention_key_ranges":
         return time_attention_key_ranges()

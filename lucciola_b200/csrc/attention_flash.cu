@@ -50,6 +50,8 @@ struct FlashParams {
   float scale_log2;                         // scale * log2(e)
   int kv_share;                             // >= 1: the cache has num_kv_heads / kv_share heads, and kv head j of this launch
                                             // reads cache head j / kv_share (several groups of query heads on one cached head)
+  const float* slopes;                      // optional [num_q_heads]: the score of key j for the query at position i is
+  float inv_scale;                          // lowered by slopes[h] * (i - j); 1 / scale brings that into the raw score's units
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
@@ -292,11 +294,13 @@ flash_attention_kernel(FlashParams p) {
   const int warp_row0 = KEYSPLIT ? 0 : warp * 16;
   const int r0 = warp_row0 + (lane >> 2);
   int row_pos[2], row_lo[2];
+  float row_bias[2];                    // the distance slope of each row's head, in the raw score's units
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = r0 + 8 * h;
     row_pos[h] = r < rows ? pos0 + r / G : -1;                  // -1: no key passes the mask
     row_lo[h] = p.window > 0 ? max(0, row_pos[h] - p.window + 1) : 0;
+    row_bias[h] = (p.slopes && r < rows) ? p.slopes[kvh * G + r % G] * p.inv_scale : 0.f;
   }
   const bool warp_active = warp_row0 < rows;
 
@@ -357,9 +361,10 @@ flash_attention_kernel(FlashParams p) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int h = e >> 1;
-        if (need_mask) {
+        if (need_mask || p.slopes) {
           const int j = kbase + key0 + nb * 8 + (lane & 3) * 2 + (e & 1);
-          if (j > row_pos[h] || j < row_lo[h] || j >= kend) s[nb][e] = -INFINITY;
+          s[nb][e] = fmaf(-row_bias[h], (float)(row_pos[h] - j), s[nb][e]);
+          if (need_mask && (j > row_pos[h] || j < row_lo[h] || j >= kend)) s[nb][e] = -INFINITY;
         }
         m_new[h] = fmaxf(m_new[h], s[nb][e]);
       }
@@ -607,11 +612,13 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
 
   const int r0 = lane >> 2;
   int row_pos[2], row_lo[2];
+  float row_bias[2];                    // the distance slope of each row's head, in the raw score's units
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = r0 + 8 * h;
     row_pos[h] = r < rows ? pos0 + r / G : -1;                  // -1: no key passes the mask
     row_lo[h] = p.window > 0 ? max(0, row_pos[h] - p.window + 1) : 0;
+    row_bias[h] = (p.slopes && r < rows) ? p.slopes[kvh * G + r % G] * p.inv_scale : 0.f;
   }
   cp_async_wait<0>();
   keysplit_sync<true>();
@@ -671,9 +678,10 @@ flash_decode_tma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_c
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int h = e >> 1;
-        if (need_mask) {
+        if (need_mask || p.slopes) {
           const int j = kbase + key0 + nb * 8 + (lane & 3) * 2 + (e & 1);
-          if (j > row_pos[h] || j < row_lo[h] || j >= kend) s[nb][e] = -INFINITY;
+          s[nb][e] = fmaf(-row_bias[h], (float)(row_pos[h] - j), s[nb][e]);
+          if (need_mask && (j > row_pos[h] || j < row_lo[h] || j >= kend)) s[nb][e] = -INFINITY;
         }
         m_new[h] = fmaxf(m_new[h], s[nb][e]);
       }
@@ -894,11 +902,13 @@ LB_EXPORT long long lb_attention_flash_workspace(int num_tiles, int num_kv_heads
 // tokens * (nq / nkv) <= part_rows <= 64.  workspace: float32, needed when splits > 1.
 // kv_share >= 1: the pools hold num_kv_heads / kv_share heads and kv head j reads pool head j / kv_share, so that
 // many query heads on one cached head can be cut into groups of at most 16 (the tiles of the decode kernels).
+// slopes (optional, float32 [nq]): a linear distance bias, score(i, j) = (q_i . k_j) * scale - slopes[h] * (i - j).
 LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, const void* v_cache,
                                  const int* positions, const int* block_table, const void* tiles, int num_tiles,
                                  int num_q_heads, int num_kv_heads, int head_dim, int page_size, int max_pages,
                                  int num_pages, int window, float scale, int splits, int part_rows, float* workspace,
-                                 long long workspace_elems, int kv_share, cudaStream_t stream) {
+                                 long long workspace_elems, int kv_share, const float* slopes, cudaStream_t stream) {
+  LB_CHECK_ARG(slopes == nullptr || scale > 0.f, "attention_flash: a distance bias needs a positive scale");
   LB_CHECK_ARG(num_q_heads > 0 && num_kv_heads > 0 && num_q_heads % num_kv_heads == 0,
                "attention_flash: %d query heads are not a multiple of %d kv heads", num_q_heads, num_kv_heads);
   LB_CHECK_ARG(kv_share >= 1 && num_kv_heads % kv_share == 0, "attention_flash: %d kv heads cannot share cached heads %d by %d",
@@ -935,6 +945,7 @@ LB_EXPORT int lb_attention_flash(const void* q, void* out, const void* k_cache, 
   p.page_shift = page_shift;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.kv_share = kv_share;
+  p.slopes = slopes; p.inv_scale = slopes ? 1.f / scale : 0.f;
   dim3 grid(num_tiles, num_kv_heads, splits);
   const int dp = head_dim <= 64 ? 64 : 128;
   const int smem = part_rows <= 16 ? (lb::FA_ROWS + 2 * lb::FA_STAGES * lb::FA_KEYS) * dp * 2   // query tile + 3 stages

@@ -76,7 +76,7 @@ _SIGNATURES = {
     "lb_zero_rows": [c_void_p, c_longlong, c_int, c_void_p, c_int, c_void_p],
     "lb_gemm_tcgen05_heads": [c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p],
     "lb_attention_flash": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
-                           c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p],
+                           c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p],
     "lb_attention_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                              c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong, c_void_p],
     "lb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
@@ -766,7 +766,8 @@ def attention_wide_clusters(head_dim: int) -> int:
 def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                     positions: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor, max_rows: int,
                     num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float,
-                    splits: int, stream: int, force_workspace: bool = False, tma: bool = True, kv_share: int = 1) -> None:
+                    splits: int, stream: int, force_workspace: bool = False, tma: bool = True, kv_share: int = 1,
+                    slopes: torch.Tensor | None = None) -> None:
     """Tensor-core attention over pages.  tiles: int32 [n, 4] of (first token, tokens, request index, 0).
     `kv_share` > 1: the pools hold num_kv_heads / kv_share heads, and kv head j of this call reads pool head j // kv_share
     (many query heads on one cached head, cut into groups of at most 16 so that decoded tokens fit the decode kernel's tiles).
@@ -789,7 +790,7 @@ def attention_flash(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v
     _call("lb_attention_flash", q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
           positions.data_ptr(), block_table.data_ptr(), tiles.data_ptr(), n, num_q_heads, num_kv_heads, head_dim,
           page_size, block_table.shape[1], k_cache.shape[0] if tma else 0, window, scale,
-          -splits if force_workspace else splits, max_rows, _ptr(ws), ws_elems, kv_share, stream)
+          -splits if force_workspace else splits, max_rows, _ptr(ws), ws_elems, kv_share, _ptr(slopes), stream)
 
 
 def attention_tcgen05_ok(q: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
@@ -853,8 +854,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
     sizes) to the mma.sync kernels; everything else, and every step without a plan, goes to the plain kernel.
     `kv_share` > 1: the plan's lists other than "big" were made for groups of num_q_heads / (num_kv_heads * kv_share)
     query heads, kv_share of which read one cached head (see attention_flash)."""
-    if plan is None or (v_dim and v_dim != head_dim) or slopes is not None or not attention_flash_ok(q, num_q_heads, num_kv_heads * kv_share, head_dim):
-        # value heads of another size than the keys' and a distance bias are the plain kernel's alone
+    if plan is None or (v_dim and v_dim != head_dim) or not attention_flash_ok(q, num_q_heads, num_kv_heads * kv_share, head_dim):
+        # value heads of another size than the keys' are the plain kernel's alone
         attention_plain(q, out, k_cache, v_cache, step.positions, step.token_seq, step.block_tables[group],
                         num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream, v_dim=v_dim, slopes=slopes)
         return
@@ -862,7 +863,10 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
     longest = step.span_hint or step.max_context_len                 # a recorded step plans for a bucket of lengths
     span = min(longest, window + step.max_q_len) if window > 0 else longest
     kinds = ["all"]
-    if "big" in meta and attention_tcgen05_ok(q, num_q_heads, num_kv_heads, head_dim, page_size,
+    if slopes is not None:
+        _check(slopes, "distance slopes", torch.float32)
+    # (the tensor-memory kernel knows no distance bias: with one, portions of prompts go to the mma.sync kernel too)
+    if "big" in meta and slopes is None and attention_tcgen05_ok(q, num_q_heads, num_kv_heads, head_dim, page_size,
                                               step.block_tables[group].shape[1]):
         attention_tcgen05(q, out, k_cache, v_cache, step.positions, step.block_tables[group], meta["big"],
                           num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream,
@@ -874,4 +878,5 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
         wide = attention_wide_clusters(head_dim) if rows <= 16 and page_size in (8, 16, 32, 64, 128) else 0
         splits = attention_splits(tiles.shape[0], num_kv_heads * kv_share, span, rows, wide_clusters=wide)
         attention_flash(q, out, k_cache, v_cache, step.positions, step.block_tables[group], tiles, rows,
-                        num_q_heads, num_kv_heads * kv_share, head_dim, page_size, window, scale, splits, stream, kv_share=kv_share)
+                        num_q_heads, num_kv_heads * kv_share, head_dim, page_size, window, scale, splits, stream, kv_share=kv_share,
+                        slopes=slopes)

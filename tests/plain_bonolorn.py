@@ -16,12 +16,12 @@ import torch
 
 def sinusoid_positions(positions: torch.Tensor, width: int, base: float = 10000.0) -> torch.Tensor:
     """[T, width]: entry 2i is sin(p * base^(-2i / width)), entry 2i + 1 the cosine of the same angle."""
-    i = torch.arange(width // 2, dtype=torch.float64)
+    i = torch.arange((width + 1) // 2, dtype=torch.float64)
     angle = positions.to(torch.float64)[:, None] * base ** (-2.0 * i / width)[None, :]
-    out = torch.zeros(positions.shape[0], width, dtype=torch.float64)
+    out = torch.zeros(positions.shape[0], 2 * i.shape[0], dtype=torch.float64)
     out[:, 0::2] = torch.sin(angle)
     out[:, 1::2] = torch.cos(angle)
-    return out
+    return out[:, :width]                    # an odd width ends on a sine
 
 
 def layer_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -51,8 +51,8 @@ def distance_slopes(heads: int) -> torch.Tensor:
 def window_attention(h: torch.Tensor, w: dict, heads: int, kv_heads: int, dim: int, vdim: int, scale: float, window: int,
                      eps: float, start: int = 0, keys_before: torch.Tensor | None = None,
                      values_before: torch.Tensor | None = None):
-    """Grouped-query softmax attention with normed queries and keys, a linear distance bias, a sliding window and a
-    sigmoid gate per head.  w: q, k, v, q.norm, k.norm, g, o.  The tokens of h stand at positions start, start + 1, ...;
+    """Grouped-query softmax attention with normed queries and keys, a linear distance bias, a sliding window (0: none)
+    and a sigmoid gate per head.  w: q, k, v, q.norm, k.norm, g, o.  The tokens of h stand at positions start, start + 1, ...;
     keys_before / values_before [start, kv_heads, *] are the normed keys and the values of the positions before.
     Returns (output [T, width], all keys, all values)."""
     T = h.shape[0]
@@ -67,7 +67,7 @@ def window_attention(h: torch.Tensor, w: dict, heads: int, kv_heads: int, dim: i
     per = heads // kv_heads
     for t in range(T):
         i = start + t
-        lo = max(0, i - window + 1)                                        # 0 <= i - j < window
+        lo = max(0, i - window + 1) if window > 0 else 0                  # 0 <= i - j < window; no window: every key before
         js = torch.arange(lo, i + 1)
         for hd in range(heads):
             g = hd // per
@@ -170,7 +170,7 @@ class PlainBonolorn:
             mx, st = layer["mixer"], state["layers"][i]
             L, R = mx["left"], mx["right"]
             a, st["k"], st["v"] = window_attention(x, self._sub(f"l{i}.mix.left."), L["heads"], L["kv_heads"], L["dim"], L["vdim"],
-                                                   L["scale"], L["mask"]["size"], eps, start, st["k"], st["v"])
+                                                   L["scale"], (L.get("mask") or {}).get("size", 0), eps, start, st["k"], st["v"])
             b, st["S"] = decay_attention(x, self._sub(f"l{i}.mix.right."), R["heads"], R["dim"], R["vdim"], R["decay"], eps, st["S"])
             x = x + m * layer_norm(mx["left_scale"] * a + mx["right_scale"] * b, w[f"l{i}.norm1"], eps)
             mlp = layer.get("mlp")
