@@ -119,6 +119,175 @@ static cudaError_t launch_decay_recurrence(const DecayRecurrenceParams& p, int n
   return launch(decay_recurrence_kernel<DS, TC, MAX_THREADS>, dim3((p.vdim + 31) / 32, p.heads, num_seqs), dim3(nwarps * 32), smem, stream, p);
 }
 
+
+// The same recurrence with a chunk's OUTPUTS formed side by side instead of token after token, for steps that bring many
+// tokens a sequence.  With S0 the state before a chunk of C tokens and t, j counting inside the chunk,
+//
+//   o_t = decay^(t+1) * S0^T q_t  +  sum_{j <= t} decay^(t-j) (q_t . k_j) v_j
+//
+// The first term is C independent sums over the rows of S0 (no token waits for the one before), the second needs the
+// C x C scores of the chunk, which every thread of the CTA shares.  The state itself still moves token by token,
+// S <- decay S + k_j v_j^T, the very operations of the kernel above, so the state a step leaves is the same to the last
+// bit whichever kernel ran; only the order in which an output's terms are added differs (32-bit throughout).  The raw
+// inputs of the next chunk are requested before the work on the current one and turned into q, k, v after it.
+constexpr int DC_C = 16;
+
+template <int DS, int NV>      // NV: values of v a thread holds for the next chunk, ceil(C * 32 / threads) rounded up to 2, 4, 8 or 16
+__global__ void __launch_bounds__(256) decay_chunk_kernel(DecayRecurrenceParams p) {
+  extern __shared__ __align__(16) float smem[];
+  pdl_trigger();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5, nt = blockDim.x;
+  const int dimp = nwarps * DS, ldq = dimp + 4;       // rows padded by 4 floats: the scores read 16 rows at one column
+  constexpr int PER = 2 * DC_C * DS / 32;             // raw q and k values a thread holds for the next chunk (2 C dimp / threads)
+  float* qs = smem;                                   // [C][ldq]
+  float* ks = qs + DC_C * ldq;                        // [C][ldq]
+  float* vs = ks + DC_C * ldq;                        // [C][32]
+  float* part = vs + DC_C * 32;                       // [C][nwarps][32]
+  float* wts = part + DC_C * nwarps * 32;             // [C][C + 1]
+  const int e0 = blockIdx.x * 32, e = e0 + lane, h = blockIdx.y, seq = blockIdx.z;
+  const bool e_ok = e < p.vdim;
+  const float decay = p.decay[h];
+  float pw[DC_C + 1];                                 // powers of the decay
+  pw[0] = 1.f;
+#pragma unroll
+  for (int i = 1; i <= DC_C; ++i) pw[i] = pw[i - 1] * decay;
+  const int first = p.cu_tokens[seq], n = p.cu_tokens[seq + 1] - first;
+  float* st = p.state + (((size_t)p.slots[seq] * p.heads + h) * p.dim) * p.vdim;
+  float s[DS];
+  float raw[PER], rawv[NV];
+  const int per_chunk = DC_C * dimp;                  // q (and k) values of a chunk
+  pdl_wait();
+  auto request = [&](int c0) {                        // the raw inputs of the chunk that starts at token c0
+    const int cn = min(DC_C, n - c0);
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+      const int idx = u * nt + threadIdx.x;           // 0 .. 2 * per_chunk: q then k
+      const int which = idx >= per_chunk, r = idx - which * per_chunk;
+      const int tt = r / dimp, d = r - tt * dimp;
+      raw[u] = (idx < 2 * per_chunk && tt < cn && d < p.dim)
+                   ? p.pre[(size_t)(first + c0 + tt) * p.ld + (which ? p.k_col : p.q_col) + h * p.dim + d] : -INFINITY;
+    }
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+      const int idx = u * nt + threadIdx.x, tt = idx >> 5, ee = e0 + (idx & 31);
+      rawv[u] = (idx < DC_C * 32 && tt < cn && ee < p.vdim) ? p.pre[(size_t)(first + c0 + tt) * p.ld + p.v_col + h * p.vdim + ee] : -INFINITY;
+    }
+  };
+  auto stage = [&]() {                                // silu of what was requested, into shared memory (silu(-inf) = 0)
+#pragma unroll
+    for (int u = 0; u < PER; ++u) {
+      const int idx = u * nt + threadIdx.x;
+      if (idx < 2 * per_chunk) {
+        const int which = idx >= per_chunk, r = idx - which * per_chunk;
+        const int tt = r / dimp, d = r - tt * dimp;
+        (which ? ks : qs)[tt * ldq + d] = raw[u] == -INFINITY ? 0.f : silu_f(raw[u]);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < NV; ++u) {
+      const int idx = u * nt + threadIdx.x;
+      if (idx < DC_C * 32) vs[idx] = rawv[u] == -INFINITY ? 0.f : silu_f(rawv[u]);
+    }
+  };
+#pragma unroll
+  for (int i = 0; i < DS; ++i) {
+    const int d = warp * DS + i;
+    s[i] = (d < p.dim && e_ok) ? st[(size_t)d * p.vdim + e] : 0.f;
+  }
+  if (n > 0) { request(0); stage(); }
+  __syncthreads();
+  for (int c0 = 0; c0 < n; c0 += DC_C) {
+    const int cn = min(DC_C, n - c0);
+    if (c0 + DC_C < n) request(c0 + DC_C);
+    // the part of every output that comes from the state before the chunk: C sums side by side
+    {
+      float acc[DC_C];
+#pragma unroll
+      for (int t = 0; t < DC_C; ++t) acc[t] = 0.f;
+#pragma unroll
+      for (int i4 = 0; i4 < DS; i4 += 4) {
+#pragma unroll
+        for (int t = 0; t < DC_C; ++t) {
+          const float4 q4 = *reinterpret_cast<const float4*>(qs + t * ldq + warp * DS + i4);
+          acc[t] = fmaf(s[i4 + 0], q4.x, acc[t]); acc[t] = fmaf(s[i4 + 1], q4.y, acc[t]);
+          acc[t] = fmaf(s[i4 + 2], q4.z, acc[t]); acc[t] = fmaf(s[i4 + 3], q4.w, acc[t]);
+        }
+      }
+#pragma unroll
+      for (int t = 0; t < DC_C; ++t) part[(t * nwarps + warp) * 32 + lane] = acc[t] * pw[t + 1];
+    }
+    // the state moves on, token by token
+    for (int j = 0; j < cn; ++j) {
+      const float v = vs[j * 32 + lane];
+      const float* kr = ks + j * ldq + warp * DS;
+#pragma unroll
+      for (int i4 = 0; i4 < DS; i4 += 4) {
+        const float4 k4 = *reinterpret_cast<const float4*>(kr + i4);
+        s[i4 + 0] = fmaf(decay, s[i4 + 0], k4.x * v); s[i4 + 1] = fmaf(decay, s[i4 + 1], k4.y * v);
+        s[i4 + 2] = fmaf(decay, s[i4 + 2], k4.z * v); s[i4 + 3] = fmaf(decay, s[i4 + 3], k4.w * v);
+      }
+    }
+    // the chunk's own scores, weighted by the decay over the distance: wts[t][j] = decay^(t-j) (q_t . k_j) for j <= t
+    for (int idx = threadIdx.x; idx < DC_C * DC_C; idx += nt) {
+      const int t = idx / DC_C, j = idx - t * DC_C;
+      float a = 0.f;
+      if (j <= t && t < cn) {
+        const float* qr = qs + t * ldq;
+        const float* kr = ks + j * ldq;
+        for (int i = 0; i < dimp; i += 4) {
+          const float4 q4 = *reinterpret_cast<const float4*>(qr + i);
+          const float4 k4 = *reinterpret_cast<const float4*>(kr + i);
+          a = fmaf(q4.x, k4.x, a); a = fmaf(q4.y, k4.y, a); a = fmaf(q4.z, k4.z, a); a = fmaf(q4.w, k4.w, a);
+        }
+        float w = 1.f;                                 // decay^(t-j) by the same products as the table
+        for (int r = 0; r < t - j; ++r) w *= decay;
+        a *= w;
+      }
+      wts[t * (DC_C + 1) + j] = a;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < cn * 32; idx += nt) {
+      const int t = idx >> 5, l = idx & 31, ee = e0 + l;
+      if (ee >= p.vdim) continue;
+      float o = 0.f;
+      for (int w = 0; w < nwarps; ++w) o += part[(t * nwarps + w) * 32 + l];
+      for (int j = 0; j <= t; ++j) o = fmaf(wts[t * (DC_C + 1) + j], vs[j * 32 + l], o);
+      p.out[(size_t)(first + c0 + t) * (p.heads * p.vdim) + h * p.vdim + ee] = o;
+    }
+    __syncthreads();
+    if (c0 + DC_C < n) stage();
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < DS; ++i) {
+    const int d = warp * DS + i;
+    if (d < p.dim && e_ok) st[(size_t)d * p.vdim + e] = s[i];
+  }
+}
+
+template <int DS, int NV>
+static cudaError_t launch_decay_chunk_nv(const DecayRecurrenceParams& p, int num_seqs, int nwarps, cudaStream_t stream) {
+  const int dimp = nwarps * DS;
+  const size_t smem = (size_t)(2 * DC_C * (dimp + 4) + DC_C * 32 + DC_C * nwarps * 32 + DC_C * (DC_C + 1)) * sizeof(float);
+  static size_t allowed = 48 * 1024;
+  if (smem > allowed) {
+    const cudaError_t e = cudaFuncSetAttribute(decay_chunk_kernel<DS, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    allowed = smem;
+  }
+  return launch(decay_chunk_kernel<DS, NV>, dim3((p.vdim + 31) / 32, p.heads, num_seqs), dim3(nwarps * 32), smem, stream, p);
+}
+
+template <int DS>
+static cudaError_t launch_decay_chunk(const DecayRecurrenceParams& p, int num_seqs, cudaStream_t stream) {
+  const int nwarps = (p.dim + DS - 1) / DS;
+  const int nv = (DC_C * 32 + nwarps * 32 - 1) / (nwarps * 32);
+  if (nv <= 2) return launch_decay_chunk_nv<DS, 2>(p, num_seqs, nwarps, stream);
+  if (nv <= 4) return launch_decay_chunk_nv<DS, 4>(p, num_seqs, nwarps, stream);
+  if (nv <= 8) return launch_decay_chunk_nv<DS, 8>(p, num_seqs, nwarps, stream);
+  return launch_decay_chunk_nv<DS, 16>(p, num_seqs, nwarps, stream);
+}
+
 // out[t, :] = x[t, :] * rsqrt(mean(x[t]^2) + eps) * weight * sigmoid(gate[t, :]) * scale: the heads' outputs normed
 // together and gated elementwise.  out may be a column range of a wider matrix (row stride out_ld).
 template <typename TO>
@@ -153,11 +322,15 @@ __global__ void head_gate_kernel(T* __restrict__ out, long long out_ld, const T*
 
 }  // namespace lb
 
-// max_tokens_a_seq: the most tokens any sequence brings, if the host knows it (0: unknown); it only chooses the
-// chunk's size, which never shows in a result.
+// max_tokens_a_seq: the most tokens any sequence brings, if the host knows it (0: unknown); in the token-by-token kernel
+// it only chooses the chunk's size, which never shows in a result.
+// side_by_side: 1 lets steps of more than 4 tokens a sequence (heads of up to 256 rows) run in the kernel that forms a
+// chunk's outputs side by side: the same state to the last bit, outputs equal within 32-bit rounding (their terms are
+// added in another order), several times faster.  0 keeps every step in the token-by-token kernel, whose outputs do not
+// depend on how a sequence was cut into steps.
 LB_EXPORT int lb_decay_recurrence(const float* pre, long long ld, int q_col, int k_col, int v_col, const float* decay,
                                   float* state, float* out, const int* cu_tokens, const int* slots, int num_seqs,
-                                  int heads, int dim, int vdim, int max_tokens_a_seq, cudaStream_t stream) {
+                                  int heads, int dim, int vdim, int max_tokens_a_seq, int side_by_side, cudaStream_t stream) {
   LB_CHECK_ARG(pre && decay && state && out && cu_tokens && slots, "decay_recurrence: null argument");
   LB_CHECK_ARG(num_seqs >= 0 && heads > 0 && heads <= 65535 && dim > 0 && dim <= 1024 && vdim > 0 && num_seqs <= 65535,
                "decay_recurrence: bad sizes seqs=%d heads=%d dim=%d vdim=%d (dim at most 1024)", num_seqs, heads, dim, vdim);
@@ -167,6 +340,15 @@ LB_EXPORT int lb_decay_recurrence(const float* pre, long long ld, int q_col, int
   p.state = state; p.out = out; p.cu_tokens = cu_tokens; p.slots = slots; p.heads = heads; p.dim = dim; p.vdim = vdim;
   const bool few = max_tokens_a_seq > 0 && max_tokens_a_seq <= 4;
   cudaError_t e;
+  if (side_by_side && !few && dim <= 256) {
+    if (dim <= 32) e = lb::launch_decay_chunk<4>(p, num_seqs, stream);
+    else if (dim <= 64) e = lb::launch_decay_chunk<8>(p, num_seqs, stream);
+    else if (dim <= 128) e = lb::launch_decay_chunk<16>(p, num_seqs, stream);
+    else e = lb::launch_decay_chunk<32>(p, num_seqs, stream);
+    if (e != cudaSuccess) { lb::set_error("decay_recurrence: %s", cudaGetErrorString(e)); return 2; }
+    LB_CHECK_LAUNCH("decay_recurrence");
+    return 0;
+  }
   // rows of the state a warp keeps: as few as give at most 8 warps; heads of more than 256 rows: 32 rows a warp
   if (dim > 256) e = lb::launch_decay_recurrence<32, 4, 1024>(p, num_seqs, stream);
   else if (few) {

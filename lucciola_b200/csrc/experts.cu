@@ -143,7 +143,7 @@ __device__ __forceinline__ float expert_act(int act, float limit, float g, float
   return g / (1.f + expf(-g)) * u;
 }
 
-constexpr int EX_BM = 32, EX_BN = 64, EX_BK = 16;
+constexpr int EX_BM = 64, EX_BN = 64, EX_BK = 16;
 
 struct ExpertGemmParams {
   void* y; const void* x; const void* w;
@@ -154,7 +154,7 @@ struct ExpertGemmParams {
   int gated, act; float limit;
 };
 
-// ordinary pipes, any types: a tile of 32 places x 64 output columns, k in increasing order by one thread an element
+// ordinary pipes, any types: a tile of 64 places x 64 output columns, k in increasing order by one thread an element
 template <typename TX, typename TW, typename TY, bool GATED>
 __global__ void __launch_bounds__(256) expert_gemm_plain_kernel(ExpertGemmParams p) {
   __shared__ float xs[EX_BK][EX_BM + 4];
@@ -175,16 +175,16 @@ __global__ void __launch_bounds__(256) expert_gemm_plain_kernel(ExpertGemmParams
     src_row[tid] = place < r1 ? (p.gather ? p.pair_at[place] / p.top : place) : -1;
   }
   __syncthreads();
-  const int tr = tid / 16, tc = tid % 16;               // rows tr * 2 .., columns tc * 4 ..
-  float acc[2][4], acc2[2][4];
+  const int tr = tid / 16, tc = tid % 16;               // rows tr * 4 .., columns tc * 4 ..
+  float acc[4][4], acc2[4][4];
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < 4; ++i)
 #pragma unroll
     for (int j = 0; j < 4; ++j) { acc[i][j] = 0.f; acc2[i][j] = 0.f; }
   for (int k0 = 0; k0 < p.K; k0 += EX_BK) {
 #pragma unroll
-    for (int it = 0; it < 2; ++it) {
-      const int idx = tid + it * 256;                   // 512 = 32 rows x 16
+    for (int it = 0; it < 4; ++it) {
+      const int idx = tid + it * 256;                   // 1024 = 64 rows x 16
       const int r = idx / EX_BK, c = idx % EX_BK;
       const int row = src_row[r], gk = k0 + c;
       xs[c][r] = (row >= 0 && gk < p.K) ? to_f32(x[(size_t)row * p.ldx + gk]) : 0.f;
@@ -201,13 +201,13 @@ __global__ void __launch_bounds__(256) expert_gemm_plain_kernel(ExpertGemmParams
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < EX_BK; ++kk) {
-      float a[2], b[4], b2[4];
+      float a[4], b[4], b2[4];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) a[i] = xs[kk][tr * 2 + i];
+      for (int i = 0; i < 4; ++i) a[i] = xs[kk][tr * 4 + i];
 #pragma unroll
       for (int j = 0; j < 4; ++j) { b[j] = ws[0][kk][tc * 4 + j]; b2[j] = GATED ? ws[1][kk][tc * 4 + j] : 0.f; }
 #pragma unroll
-      for (int i = 0; i < 2; ++i)
+      for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
@@ -218,8 +218,8 @@ __global__ void __launch_bounds__(256) expert_gemm_plain_kernel(ExpertGemmParams
   }
   TY* y = (TY*)p.y;
 #pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const int place = r0 + tr * 2 + i;
+  for (int i = 0; i < 4; ++i) {
+    const int place = r0 + tr * 4 + i;
     if (place >= r1) continue;
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -231,21 +231,31 @@ __global__ void __launch_bounds__(256) expert_gemm_plain_kernel(ExpertGemmParams
   }
 }
 
-// tensor cores (mma.sync m16n8k16), bfloat16 operands, 32-bit sums: a tile of 32 places x 64 output columns a CTA of
-// four warps (warp w: rows (w & 1) * 16 .., columns (w >> 1) * 32 ..); K in blocks of 64 through shared memory.  K a
-// multiple of 8, 16-byte aligned rows.
-constexpr int EM_BM = 32, EM_BN = 64, EM_BK = 64, EM_LD = EM_BK + 8;
+// tensor cores (mma.sync m16n8k16), bfloat16 operands, 32-bit sums: a tile of 64 places x 128 output columns a CTA of
+// eight warps (warp w: rows (w & 1) * 32 .., columns (w >> 1) * 32 ..); K in blocks of 32 through two stages of shared
+// memory that 16-byte asynchronous copies fill while the tensor cores work on the other.  K a multiple of 8, 16-byte
+// aligned rows.
+constexpr int EM_BM = 64, EM_BN = 128, EM_BK = 32, EM_LD = EM_BK + 8, EM_STAGES = 2;
 
 __device__ __forceinline__ void ex_mma_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
+__device__ __forceinline__ void ex_cp_async16(void* dst, const void* src, bool valid) {
+  const int n = valid ? 16 : 0;             // 0: the 16 bytes are filled with zeros, nothing is read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(n) : "memory");
+}
+
+template <bool GATED>
+constexpr int expert_mma_smem() { return EM_STAGES * (EM_BM + (GATED ? 2 : 1) * EM_BN) * EM_LD * 2; }
 
 template <typename TY, bool GATED>
-__global__ void __launch_bounds__(128) expert_gemm_mma_kernel(ExpertGemmParams p) {
-  __shared__ __align__(16) bf16 As[EM_BM][EM_LD];
-  __shared__ __align__(16) bf16 Bs[GATED ? 2 : 1][EM_BN][EM_LD];
+__global__ void __launch_bounds__(256) expert_gemm_mma_kernel(ExpertGemmParams p) {
+  extern __shared__ __align__(16) uint8_t ex_smem[];
+  constexpr int NB = GATED ? 2 : 1;
+  bf16* As = reinterpret_cast<bf16*>(ex_smem);                    // [stage][BM][LD]
+  bf16* Bs = As + EM_STAGES * EM_BM * EM_LD;                      // [stage][NB][BN][LD]
   __shared__ int src_row[EM_BM];
   pdl_trigger();
   pdl_wait();
@@ -254,7 +264,7 @@ __global__ void __launch_bounds__(128) expert_gemm_mma_kernel(ExpertGemmParams p
   const int e = m[0], r0 = m[1], r1 = m[2];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
-  const int wm = (warp & 1) * 16, wn = (warp >> 1) * 32;
+  const int wm = (warp & 1) * 32, wn = (warp >> 1) * 32;
   const int ncols = GATED ? p.N / 2 : p.N;
   const int n0 = blockIdx.x * EM_BN;
   const bf16* x = (const bf16*)p.x;
@@ -264,74 +274,81 @@ __global__ void __launch_bounds__(128) expert_gemm_mma_kernel(ExpertGemmParams p
     src_row[tid] = place < r1 ? (p.gather ? p.pair_at[place] / p.top : place) : -1;
   }
   __syncthreads();
-  float acc[4][4], acc2[4][4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i)
-#pragma unroll
-    for (int j = 0; j < 4; ++j) { acc[i][j] = 0.f; acc2[i][j] = 0.f; }
-  for (int k0 = 0; k0 < p.K; k0 += EM_BK) {
+  const int a_r = tid >> 2, a_c = (tid & 3) * 8;                  // this thread's piece of A: 64 rows x 4 pieces
+  const int a_row = src_row[a_r];
+  auto load_stage = [&](int st, int k0) {
+    ex_cp_async16(As + (st * EM_BM + a_r) * EM_LD + a_c, a_row >= 0 ? x + (size_t)a_row * p.ldx + k0 + a_c : x, a_row >= 0 && k0 + a_c < p.K);
 #pragma unroll
     for (int it = 0; it < 2; ++it) {
-      const int idx = tid + it * 128;                 // 256 pieces of 8 values: 32 rows x 8
-      const int r = idx >> 3, c = (idx & 7) * 8;
-      uint4 va = make_uint4(0u, 0u, 0u, 0u);
-      const int row = src_row[r];
-      if (row >= 0 && k0 + c < p.K) va = *reinterpret_cast<const uint4*>(x + (size_t)row * p.ldx + k0 + c);
-      *reinterpret_cast<uint4*>(&As[r][c]) = va;
+      const int idx = tid + it * 256, r = idx >> 2, c = (idx & 3) * 8;   // 128 rows x 4 pieces
+      const bool ok = n0 + r < ncols && k0 + c < p.K;
+      ex_cp_async16(Bs + ((st * NB + 0) * EM_BN + r) * EM_LD + c, ok ? w + (size_t)(n0 + r) * p.K + k0 + c : w, ok);
+      if (GATED) ex_cp_async16(Bs + ((st * NB + 1) * EM_BN + r) * EM_LD + c, ok ? w + (size_t)(ncols + n0 + r) * p.K + k0 + c : w, ok);
     }
+  };
+  float acc[2][4][4], acc2[GATED ? 2 : 1][4][4];
 #pragma unroll
-    for (int it = 0; it < 4; ++it) {
-      const int idx = tid + it * 128;                 // 512 pieces: 64 rows x 8
-      const int r = idx >> 3, c = (idx & 7) * 8;
-      uint4 vb = make_uint4(0u, 0u, 0u, 0u), vb2 = vb;
-      if (n0 + r < ncols && k0 + c < p.K) {
-        vb = *reinterpret_cast<const uint4*>(w + (size_t)(n0 + r) * p.K + k0 + c);
-        if (GATED) vb2 = *reinterpret_cast<const uint4*>(w + (size_t)(ncols + n0 + r) * p.K + k0 + c);
-      }
-      *reinterpret_cast<uint4*>(&Bs[0][r][c]) = vb;
-      if (GATED) *reinterpret_cast<uint4*>(&Bs[1][r][c]) = vb2;
-    }
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int k = 0; k < 4; ++k) { acc[i][j][k] = 0.f; if (GATED) acc2[i][j][k] = 0.f; }
+  const int nk = (p.K + EM_BK - 1) / EM_BK;
+  load_stage(0, 0);
+  asm volatile("cp.async.commit_group;" ::: "memory");
+  for (int kb = 0; kb < nk; ++kb) {
+    const int st = kb & 1;
+    if (kb + 1 < nk) load_stage(st ^ 1, (kb + 1) * EM_BK);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    asm volatile("cp.async.wait_group 1;" ::: "memory");            // block kb has landed (the group after it may be in flight)
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < EM_BK; kk += 16) {
-      uint32_t a[4];
-      const bf16* ar = &As[wm + g][kk + 2 * t4];
-      a[0] = *reinterpret_cast<const uint32_t*>(ar);
-      a[1] = *reinterpret_cast<const uint32_t*>(ar + 8 * EM_LD);
-      a[2] = *reinterpret_cast<const uint32_t*>(ar + 8);
-      a[3] = *reinterpret_cast<const uint32_t*>(ar + 8 * EM_LD + 8);
+      uint32_t a[2][4];
+#pragma unroll
+      for (int mi = 0; mi < 2; ++mi) {
+        const bf16* ar = As + (st * EM_BM + wm + mi * 16 + g) * EM_LD + kk + 2 * t4;
+        a[mi][0] = *reinterpret_cast<const uint32_t*>(ar);
+        a[mi][1] = *reinterpret_cast<const uint32_t*>(ar + 8 * EM_LD);
+        a[mi][2] = *reinterpret_cast<const uint32_t*>(ar + 8);
+        a[mi][3] = *reinterpret_cast<const uint32_t*>(ar + 8 * EM_LD + 8);
+      }
 #pragma unroll
       for (int nb = 0; nb < 4; ++nb) {
         uint32_t bb[2];
-        const bf16* br = &Bs[0][wn + nb * 8 + g][kk + 2 * t4];
+        const bf16* br = Bs + ((st * NB + 0) * EM_BN + wn + nb * 8 + g) * EM_LD + kk + 2 * t4;
         bb[0] = *reinterpret_cast<const uint32_t*>(br);
         bb[1] = *reinterpret_cast<const uint32_t*>(br + 8);
-        ex_mma_16816(acc[nb], a, bb);
+        ex_mma_16816(acc[0][nb], a[0], bb);
+        ex_mma_16816(acc[1][nb], a[1], bb);
         if (GATED) {
-          const bf16* br2 = &Bs[1][wn + nb * 8 + g][kk + 2 * t4];
+          const bf16* br2 = Bs + ((st * NB + 1) * EM_BN + wn + nb * 8 + g) * EM_LD + kk + 2 * t4;
           bb[0] = *reinterpret_cast<const uint32_t*>(br2);
           bb[1] = *reinterpret_cast<const uint32_t*>(br2 + 8);
-          ex_mma_16816(acc2[nb], a, bb);
+          ex_mma_16816(acc2[0][nb], a[0], bb);
+          ex_mma_16816(acc2[1][nb], a[1], bb);
         }
       }
     }
-    __syncthreads();
+    __syncthreads();                                                // the stage may be filled again
   }
   TY* y = (TY*)p.y;
 #pragma unroll
-  for (int nb = 0; nb < 4; ++nb)
+  for (int mi = 0; mi < 2; ++mi)
 #pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int place = r0 + wm + g + 8 * half;
-      if (place >= r1) continue;
+    for (int nb = 0; nb < 4; ++nb)
 #pragma unroll
-      for (int j = 0; j < 2; ++j) {
-        const int n = n0 + wn + nb * 8 + 2 * t4 + j;
-        if (n >= ncols) continue;
-        const float v = GATED ? expert_act(p.act, p.limit, acc[nb][2 * half + j], acc2[nb][2 * half + j]) : acc[nb][2 * half + j];
-        y[(size_t)place * p.ldy + n] = from_f32<TY>(v);
+      for (int half = 0; half < 2; ++half) {
+        const int place = r0 + wm + mi * 16 + g + 8 * half;
+        if (place >= r1) continue;
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int n = n0 + wn + nb * 8 + 2 * t4 + j;
+          if (n >= ncols) continue;
+          const float v = GATED ? expert_act(p.act, p.limit, acc[mi][nb][2 * half + j], acc2[mi][nb][2 * half + j]) : acc[mi][nb][2 * half + j];
+          y[(size_t)place * p.ldy + n] = from_f32<TY>(v);
+        }
       }
-    }
 }
 
 // ---- combine ---------------------------------------------------------------------------------------------------
@@ -401,9 +418,15 @@ LB_EXPORT int lb_expert_gemm(void* y, int y_dtype, const void* x, int x_dtype, c
   const bool mma = fast && x_dtype == LB_BF16 && w_dtype == LB_BF16 && K % 8 == 0 && ldx % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0;
   if (mma) {
     dim3 grid((ncols + lb::EM_BN - 1) / lb::EM_BN, max_tiles);
+    static bool attr_set = false;
+    if (!attr_set) {       // the gated kernel's two stages need more shared memory than a launch gets unasked
+      cudaFuncSetAttribute(lb::expert_gemm_mma_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::expert_mma_smem<true>());
+      cudaFuncSetAttribute(lb::expert_gemm_mma_kernel<lb::bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::expert_mma_smem<true>());
+      attr_set = true;
+    }
     LB_DISPATCH_DTYPE(y_dtype, TY, {
-      if (gated) lb::launch(lb::expert_gemm_mma_kernel<TY, true>, grid, dim3(128), 0, stream, p);
-      else lb::launch(lb::expert_gemm_mma_kernel<TY, false>, grid, dim3(128), 0, stream, p);
+      if (gated) lb::launch(lb::expert_gemm_mma_kernel<TY, true>, grid, dim3(256), lb::expert_mma_smem<true>(), stream, p);
+      else lb::launch(lb::expert_gemm_mma_kernel<TY, false>, grid, dim3(256), lb::expert_mma_smem<false>(), stream, p);
     })
   } else {
     dim3 grid((ncols + lb::EX_BN - 1) / lb::EX_BN, max_tiles);

@@ -61,7 +61,8 @@ def build_bonolorn(cfg: BonolornConfig, rt: Runtime) -> DecoderModel:
     final_norm = LayerNorm(rt, "final.norm", W, eps)
     head = OutputHead(rt, "lm_head", cfg.vocab, W, embedding)
     # positions have no limit of their own (max_positions 0): the engine's options or its pool of pages set one
-    return DecoderModel(rt, embedding, blocks, calls, final_norm, head, cfg.vocab, 0, cfg.eos_token_ids)
+    unused = [f"l{i}.norm2" for i, l in enumerate(cfg.layers) if l.mlp is None]      # the norm of a feed-forward that is not there
+    return DecoderModel(rt, embedding, blocks, calls, final_norm, head, cfg.vocab, 0, cfg.eos_token_ids, ignored_names=unused)
 
 
 register_architecture(BonolornConfig.ARCHITECTURE, BonolornConfig.from_dict, build_bonolorn, replace=True)

@@ -26,12 +26,14 @@ class DecoderModel(Part):
     recordable = True
 
     def __init__(self, rt: Runtime, embedding: TokenEmbedding, blocks: Sequence[Block], calls: Sequence[LayerCall],
-                 final_norm: Norm, head: OutputHead, vocab_size: int, max_positions: int, eos_token_ids: Sequence[int] = ()):
+                 final_norm: Norm, head: OutputHead, vocab_size: int, max_positions: int, eos_token_ids: Sequence[int] = (),
+                 ignored_names: Sequence[str] = ()):
         self.rt = rt
         self.embedding, self.blocks, self.calls = embedding, list(blocks), list(calls)
         self.final_norm, self.head = final_norm, head
         self.vocab_size, self.max_positions = vocab_size, max_positions
         self.eos_token_ids = tuple(eos_token_ids)
+        self._ignored = list(ignored_names)      # tensors a checkpoint may carry that this model has no use for
         self._check_calls()
 
     def _check_calls(self) -> None:
@@ -58,7 +60,7 @@ class DecoderModel(Part):
         return [self.embedding, *self.blocks, self.final_norm, self.head]
 
     def ignored_names(self) -> list[str]:
-        return self.head.ignored_names()
+        return self.head.ignored_names() + self._ignored
 
     def cache_requests(self) -> list[KVPages | StateSlot | None | tuple]:
         """What each cache id has to hold, as asked by the block that writes it (its mixer's needs, and the block's own)."""

@@ -36,7 +36,7 @@ _SIGNATURES = {
                          c_int, c_int, c_void_p],
     "lb_round_copy": [c_void_p, c_int, c_void_p, c_longlong, c_void_p],
     "lb_decay_recurrence": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                            c_int, c_int, c_int, c_int, c_int, c_void_p],
+                            c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     "lb_rmsnorm_gated": [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_float, c_float, c_int, c_int,
                          c_void_p],
     "lb_head_gate": [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_longlong, c_float, c_int, c_int, c_int, c_void_p],
@@ -544,16 +544,20 @@ def round_copy(out: torch.Tensor, x: torch.Tensor, stream: int) -> None:
 
 
 def decay_recurrence(pre: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor,
-                     out: torch.Tensor, step, heads: int, dim: int, vdim: int, stream: int, max_tokens_a_seq: int = 0) -> None:
+                     out: torch.Tensor, step, heads: int, dim: int, vdim: int, stream: int, max_tokens_a_seq: int = 0,
+                     side_by_side: bool = False) -> None:
     """Linear attention with a fixed decay per head over this step's tokens: S <- decay_h S + k v^T, out = S^T q with
     q, k, v = silu of the columns of `pre` (float32, row-strided) at q_col, k_col, v_col; state [slots + 1, heads, dim, vdim]
-    float32 is read and written at each sequence's slot; out [T, heads * vdim] float32."""
+    float32 is read and written at each sequence's slot; out [T, heads * vdim] float32.
+    `side_by_side`: steps of more than 4 tokens a sequence may form the outputs of 16 tokens at a time from the state
+    before them and the tokens' own scores (32-bit, the same state, outputs equal within rounding, several times faster);
+    without it every output's sum has one order however the sequence is cut."""
     _check(decay, "decay", torch.float32); _check(state, "recurrent state", torch.float32); _check(out, "recurrence output", torch.float32)
     if pre.dtype != torch.float32 or pre.stride(1) != 1 or not pre.is_cuda:
         raise KernelError("the input projections must be float32 on the GPU with unit column stride")
     _call("lb_decay_recurrence", pre.data_ptr(), pre.stride(0), q_col, k_col, v_col, decay.data_ptr(), state.data_ptr(),
           out.data_ptr(), step.cu_tokens.data_ptr(), step.state_slots.data_ptr(), step.num_seqs, heads, dim, vdim,
-          max_tokens_a_seq, stream)
+          max_tokens_a_seq, 1 if side_by_side else 0, stream)
 
 
 def rmsnorm_gated(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, scale: float, eps: float,
@@ -854,7 +858,8 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
     sizes) to the mma.sync kernels; everything else, and every step without a plan, goes to the plain kernel.
     `kv_share` > 1: the plan's lists other than "big" were made for groups of num_q_heads / (num_kv_heads * kv_share)
     query heads, kv_share of which read one cached head (see attention_flash)."""
-    if plan is None or (v_dim and v_dim != head_dim) or not attention_flash_ok(q, num_q_heads, num_kv_heads * kv_share, head_dim):
+    if (plan is None or (v_dim and v_dim != head_dim) or (slopes is not None and not scale > 0)
+            or not attention_flash_ok(q, num_q_heads, num_kv_heads * kv_share, head_dim)):
         # value heads of another size than the keys' are the plain kernel's alone
         attention_plain(q, out, k_cache, v_cache, step.positions, step.token_seq, step.block_tables[group],
                         num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream, v_dim=v_dim, slopes=slopes)

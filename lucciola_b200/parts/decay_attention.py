@@ -7,7 +7,9 @@
 The state is 32-bit, one slot a request, zero for a new request, and is all this mixer keeps of the past: prompts,
 portions and decoded tokens go through the same kernel, which walks a sequence's tokens of the step in order from the
 state the step before left.  W_q | W_k | W_v | W_g are one product with 32-bit output; the activations, the recurrence,
-the norm and the gate are computed in 32-bit.
+the norm and the gate are computed in 32-bit.  In the bfloat16 engine steps with many tokens a sequence form the
+outputs of 16 tokens side by side (still 32-bit, the same state); the 32-bit engine walks every step token by token,
+so its results do not depend on how a prompt was cut.
 
 Beside forward(), the mixer offers its three steps apart (in_names / in_sizes, inner, `o`), so that a mixer that runs
 it beside another may stack their products (see SideBySideMixer).
@@ -72,7 +74,7 @@ class DecayLinearAttention(Mixer):
         T = pre.shape[0]
         o = rt.empty((T, self.inner_size), torch.float32)
         ops.decay_recurrence(pre, 0, n, 2 * n, self.decay, cache.state, o, step, self.heads, self.dim, self.vdim, rt.stream,
-                             max_tokens_a_seq=step.max_q_len)
+                             max_tokens_a_seq=step.max_q_len, side_by_side=rt.fast_kernels)
         g0 = 2 * n + self.inner_size
         ops.rmsnorm_gated(out, o, self.norm_w, pre[:, g0:g0 + self.inner_size], out_scale, self.eps, rt.stream)
 

@@ -196,7 +196,7 @@ def random_config(seed: int) -> dict:
     that are no multiples of 4 or 8, values larger and smaller than keys, windows from one token to none, decays up to
     1, expert counts, groups and choices, layers without feed-forward, experts with and without one for every token."""
     rng = random.Random(seed)
-    width = rng.choice([24, 40, 64, 72, 96, 128, 200])
+    width = rng.choice([24, 36, 40, 64, 72, 100, 128, 200])
     layers = []
     for _ in range(rng.randint(1, 4)):
         kv = rng.choice([1, 2, 3])
