@@ -127,24 +127,41 @@ static cudaError_t launch_decay_recurrence(const DecayRecurrenceParams& p, int n
 //
 // The first term is C independent sums over the rows of S0 (no token waits for the one before), the second needs the
 // C x C scores of the chunk, which every thread of the CTA shares.  The state itself still moves token by token,
-// S <- decay S + k_j v_j^T, the very operations of the kernel above, so the state a step leaves is the same to the last
-// bit whichever kernel ran; only the order in which an output's terms are added differs (32-bit throughout).  The raw
-// inputs of the next chunk are requested before the work on the current one and turned into q, k, v after it.
+// S <- decay S + k_j v_j^T, the very operations of the kernel above; only the order in which an output's terms are
+// added differs (32-bit throughout; silu by the fast exponential and reciprocal, 2 ulp).  The raw inputs of the next
+// chunk are requested before the work on the current one and turned into q, k, v after it.
+//
+// Both terms are sums over the rows of the state (the scores are sums over the same rows of q and k), so the rows may
+// be shared out: with `row_split` R a CTA takes dim / R rows and writes its share of every output to plane r of `out`
+// ([R, T, heads * vdim]); whoever reads `out` adds the planes in order.  A prompt of one sequence then fills R times
+// as many SMs.
 constexpr int DC_C = 16;
 
+struct DecayChunkParams {
+  DecayRecurrenceParams b;
+  int row_split, rows_a_cta;              // rows_a_cta: a multiple of 4
+  long long plane;                        // elements between two planes of out
+};
+
+__device__ __forceinline__ float silu_fast(float x) { return x * __frcp_rn(1.f + __expf(-x)); }
+
 template <int DS, int NV>      // NV: values of v a thread holds for the next chunk, ceil(C * 32 / threads) rounded up to 2, 4, 8 or 16
-__global__ void __launch_bounds__(256) decay_chunk_kernel(DecayRecurrenceParams p) {
+__global__ void __launch_bounds__(256) decay_chunk_kernel(DecayChunkParams pc) {
   extern __shared__ __align__(16) float smem[];
   pdl_trigger();
+  const DecayRecurrenceParams& p = pc.b;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5, nt = blockDim.x;
   const int dimp = nwarps * DS, ldq = dimp + 4;       // rows padded by 4 floats: the scores read 16 rows at one column
   constexpr int PER = 2 * DC_C * DS / 32;             // raw q and k values a thread holds for the next chunk (2 C dimp / threads)
+  constexpr int TSTEP = 32 / DS;                      // tokens between two of a thread's values: threads / dimp
   float* qs = smem;                                   // [C][ldq]
   float* ks = qs + DC_C * ldq;                        // [C][ldq]
   float* vs = ks + DC_C * ldq;                        // [C][32]
   float* part = vs + DC_C * 32;                       // [C][nwarps][32]
   float* wts = part + DC_C * nwarps * 32;             // [C][C + 1]
-  const int e0 = blockIdx.x * 32, e = e0 + lane, h = blockIdx.y, seq = blockIdx.z;
+  const int ct = blockIdx.x / pc.row_split, rs = blockIdx.x - ct * pc.row_split;
+  const int e0 = ct * 32, e = e0 + lane, h = blockIdx.y, seq = blockIdx.z;
+  const int row0 = rs * pc.rows_a_cta, row_end = min(p.dim, row0 + pc.rows_a_cta);     // this CTA's rows of the state
   const bool e_ok = e < p.vdim;
   const float decay = p.decay[h];
   float pw[DC_C + 1];                                 // powers of the decay
@@ -153,19 +170,24 @@ __global__ void __launch_bounds__(256) decay_chunk_kernel(DecayRecurrenceParams 
   for (int i = 1; i <= DC_C; ++i) pw[i] = pw[i - 1] * decay;
   const int first = p.cu_tokens[seq], n = p.cu_tokens[seq + 1] - first;
   float* st = p.state + (((size_t)p.slots[seq] * p.heads + h) * p.dim) * p.vdim;
+  float* out = p.out + (size_t)rs * pc.plane;
   float s[DS];
   float raw[PER], rawv[NV];
-  const int per_chunk = DC_C * dimp;                  // q (and k) values of a chunk
+  // a thread's u-th raw value is q (u < PER / 2) or k at (token u' * TSTEP + tq, row td) of the chunk, u' = u mod PER / 2
+  const int tq = threadIdx.x / dimp, td = threadIdx.x - tq * dimp;
+  const bool td_ok = row0 + td < row_end;
+  const float* q_src = p.pre + p.q_col + h * p.dim + row0 + td;
+  const float* k_src = p.pre + p.k_col + h * p.dim + row0 + td;
   pdl_wait();
   auto request = [&](int c0) {                        // the raw inputs of the chunk that starts at token c0
     const int cn = min(DC_C, n - c0);
 #pragma unroll
-    for (int u = 0; u < PER; ++u) {
-      const int idx = u * nt + threadIdx.x;           // 0 .. 2 * per_chunk: q then k
-      const int which = idx >= per_chunk, r = idx - which * per_chunk;
-      const int tt = r / dimp, d = r - tt * dimp;
-      raw[u] = (idx < 2 * per_chunk && tt < cn && d < p.dim)
-                   ? p.pre[(size_t)(first + c0 + tt) * p.ld + (which ? p.k_col : p.q_col) + h * p.dim + d] : -INFINITY;
+    for (int u = 0; u < PER / 2; ++u) {
+      const int tt = u * TSTEP + tq;
+      const bool ok = tt < cn && td_ok;
+      const size_t off = (size_t)(first + c0 + tt) * p.ld;
+      raw[u] = ok ? q_src[off] : -INFINITY;
+      raw[PER / 2 + u] = ok ? k_src[off] : -INFINITY;
     }
 #pragma unroll
     for (int u = 0; u < NV; ++u) {
@@ -173,26 +195,23 @@ __global__ void __launch_bounds__(256) decay_chunk_kernel(DecayRecurrenceParams 
       rawv[u] = (idx < DC_C * 32 && tt < cn && ee < p.vdim) ? p.pre[(size_t)(first + c0 + tt) * p.ld + p.v_col + h * p.vdim + ee] : -INFINITY;
     }
   };
-  auto stage = [&]() {                                // silu of what was requested, into shared memory (silu(-inf) = 0)
+  auto stage = [&]() {                                // silu of what was requested, into shared memory (nothing requested: 0)
 #pragma unroll
-    for (int u = 0; u < PER; ++u) {
-      const int idx = u * nt + threadIdx.x;
-      if (idx < 2 * per_chunk) {
-        const int which = idx >= per_chunk, r = idx - which * per_chunk;
-        const int tt = r / dimp, d = r - tt * dimp;
-        (which ? ks : qs)[tt * ldq + d] = raw[u] == -INFINITY ? 0.f : silu_f(raw[u]);
-      }
+    for (int u = 0; u < PER / 2; ++u) {
+      const int tt = u * TSTEP + tq;
+      qs[tt * ldq + td] = raw[u] == -INFINITY ? 0.f : silu_fast(raw[u]);
+      ks[tt * ldq + td] = raw[PER / 2 + u] == -INFINITY ? 0.f : silu_fast(raw[PER / 2 + u]);
     }
 #pragma unroll
     for (int u = 0; u < NV; ++u) {
       const int idx = u * nt + threadIdx.x;
-      if (idx < DC_C * 32) vs[idx] = rawv[u] == -INFINITY ? 0.f : silu_f(rawv[u]);
+      if (idx < DC_C * 32) vs[idx] = rawv[u] == -INFINITY ? 0.f : silu_fast(rawv[u]);
     }
   };
 #pragma unroll
   for (int i = 0; i < DS; ++i) {
-    const int d = warp * DS + i;
-    s[i] = (d < p.dim && e_ok) ? st[(size_t)d * p.vdim + e] : 0.f;
+    const int d = row0 + warp * DS + i;
+    s[i] = (d < row_end && e_ok) ? st[(size_t)d * p.vdim + e] : 0.f;
   }
   if (n > 0) { request(0); stage(); }
   __syncthreads();
@@ -230,20 +249,19 @@ __global__ void __launch_bounds__(256) decay_chunk_kernel(DecayRecurrenceParams 
     // the chunk's own scores, weighted by the decay over the distance: wts[t][j] = decay^(t-j) (q_t . k_j) for j <= t
     for (int idx = threadIdx.x; idx < DC_C * DC_C; idx += nt) {
       const int t = idx / DC_C, j = idx - t * DC_C;
-      float a = 0.f;
+      float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
       if (j <= t && t < cn) {
         const float* qr = qs + t * ldq;
         const float* kr = ks + j * ldq;
         for (int i = 0; i < dimp; i += 4) {
           const float4 q4 = *reinterpret_cast<const float4*>(qr + i);
           const float4 k4 = *reinterpret_cast<const float4*>(kr + i);
-          a = fmaf(q4.x, k4.x, a); a = fmaf(q4.y, k4.y, a); a = fmaf(q4.z, k4.z, a); a = fmaf(q4.w, k4.w, a);
+          a0 = fmaf(q4.x, k4.x, a0); a1 = fmaf(q4.y, k4.y, a1); a2 = fmaf(q4.z, k4.z, a2); a3 = fmaf(q4.w, k4.w, a3);
         }
-        float w = 1.f;                                 // decay^(t-j) by the same products as the table
-        for (int r = 0; r < t - j; ++r) w *= decay;
-        a *= w;
       }
-      wts[t * (DC_C + 1) + j] = a;
+      float w = 1.f;                                   // decay^(t-j) by the same products as the table
+      for (int r = 0; r < t - j; ++r) w *= decay;
+      wts[t * (DC_C + 1) + j] = ((a0 + a1) + (a2 + a3)) * w;
     }
     __syncthreads();
     for (int idx = threadIdx.x; idx < cn * 32; idx += nt) {
@@ -252,7 +270,7 @@ __global__ void __launch_bounds__(256) decay_chunk_kernel(DecayRecurrenceParams 
       float o = 0.f;
       for (int w = 0; w < nwarps; ++w) o += part[(t * nwarps + w) * 32 + l];
       for (int j = 0; j <= t; ++j) o = fmaf(wts[t * (DC_C + 1) + j], vs[j * 32 + l], o);
-      p.out[(size_t)(first + c0 + t) * (p.heads * p.vdim) + h * p.vdim + ee] = o;
+      out[(size_t)(first + c0 + t) * (p.heads * p.vdim) + h * p.vdim + ee] = o;
     }
     __syncthreads();
     if (c0 + DC_C < n) stage();
@@ -260,13 +278,13 @@ __global__ void __launch_bounds__(256) decay_chunk_kernel(DecayRecurrenceParams 
   }
 #pragma unroll
   for (int i = 0; i < DS; ++i) {
-    const int d = warp * DS + i;
-    if (d < p.dim && e_ok) st[(size_t)d * p.vdim + e] = s[i];
+    const int d = row0 + warp * DS + i;
+    if (d < row_end && e_ok) st[(size_t)d * p.vdim + e] = s[i];
   }
 }
 
 template <int DS, int NV>
-static cudaError_t launch_decay_chunk_nv(const DecayRecurrenceParams& p, int num_seqs, int nwarps, cudaStream_t stream) {
+static cudaError_t launch_decay_chunk_nv(const DecayChunkParams& pc, int num_seqs, int nwarps, cudaStream_t stream) {
   const int dimp = nwarps * DS;
   const size_t smem = (size_t)(2 * DC_C * (dimp + 4) + DC_C * 32 + DC_C * nwarps * 32 + DC_C * (DC_C + 1)) * sizeof(float);
   static size_t allowed = 48 * 1024;
@@ -275,36 +293,42 @@ static cudaError_t launch_decay_chunk_nv(const DecayRecurrenceParams& p, int num
     if (e != cudaSuccess) return e;
     allowed = smem;
   }
-  return launch(decay_chunk_kernel<DS, NV>, dim3((p.vdim + 31) / 32, p.heads, num_seqs), dim3(nwarps * 32), smem, stream, p);
+  return launch(decay_chunk_kernel<DS, NV>, dim3(((pc.b.vdim + 31) / 32) * pc.row_split, pc.b.heads, num_seqs), dim3(nwarps * 32), smem, stream, pc);
 }
 
 template <int DS>
-static cudaError_t launch_decay_chunk(const DecayRecurrenceParams& p, int num_seqs, cudaStream_t stream) {
-  const int nwarps = (p.dim + DS - 1) / DS;
+static cudaError_t launch_decay_chunk(const DecayChunkParams& pc, int num_seqs, cudaStream_t stream) {
+  const int nwarps = (pc.rows_a_cta + DS - 1) / DS;
   const int nv = (DC_C * 32 + nwarps * 32 - 1) / (nwarps * 32);
-  if (nv <= 2) return launch_decay_chunk_nv<DS, 2>(p, num_seqs, nwarps, stream);
-  if (nv <= 4) return launch_decay_chunk_nv<DS, 4>(p, num_seqs, nwarps, stream);
-  if (nv <= 8) return launch_decay_chunk_nv<DS, 8>(p, num_seqs, nwarps, stream);
-  return launch_decay_chunk_nv<DS, 16>(p, num_seqs, nwarps, stream);
+  if (nv <= 2) return launch_decay_chunk_nv<DS, 2>(pc, num_seqs, nwarps, stream);
+  if (nv <= 4) return launch_decay_chunk_nv<DS, 4>(pc, num_seqs, nwarps, stream);
+  if (nv <= 8) return launch_decay_chunk_nv<DS, 8>(pc, num_seqs, nwarps, stream);
+  return launch_decay_chunk_nv<DS, 16>(pc, num_seqs, nwarps, stream);
 }
 
 // out[t, :] = x[t, :] * rsqrt(mean(x[t]^2) + eps) * weight * sigmoid(gate[t, :]) * scale: the heads' outputs normed
-// together and gated elementwise.  out may be a column range of a wider matrix (row stride out_ld).
+// together and gated elementwise.  out may be a column range of a wider matrix (row stride out_ld).  x may come in
+// `planes` planes (`plane` elements apart) whose sum is meant; they are added in order.
 template <typename TO>
 __global__ void rmsnorm_gated_kernel(TO* __restrict__ out, long long out_ld, const float* __restrict__ x,
                                      const float* __restrict__ weight, const float* __restrict__ gate, long long gate_ld,
-                                     float scale, float eps, int n) {
+                                     float scale, float eps, int n, int planes, long long plane) {
   __shared__ float scratch[33];
   pdl_trigger();
   pdl_wait();
   const float* r = x + (size_t)blockIdx.x * n;
   const float* g = gate + (size_t)blockIdx.x * gate_ld;
+  auto value = [&](int j) {
+    float v = r[j];
+    for (int q = 1; q < planes; ++q) v += r[(size_t)q * plane + j];
+    return v;
+  };
   float ss = 0.f;
-  for (int j = threadIdx.x; j < n; j += blockDim.x) ss += r[j] * r[j];
+  for (int j = threadIdx.x; j < n; j += blockDim.x) { const float v = value(j); ss += v * v; }
   const float inv = rsqrtf(block_sum(ss, scratch) / (float)n + eps);
   TO* o = out + (size_t)blockIdx.x * out_ld;
   for (int j = threadIdx.x; j < n; j += blockDim.x)
-    o[j] = from_f32<TO>(r[j] * inv * weight[j] * (1.f / (1.f + expf(-g[j]))) * scale);
+    o[j] = from_f32<TO>(value(j) * inv * weight[j] * (1.f / (1.f + expf(-g[j]))) * scale);
 }
 
 // out[t, h, :] = x[t, h, :] * sigmoid(gate[t, h]) * scale: one number a head
@@ -324,13 +348,24 @@ __global__ void head_gate_kernel(T* __restrict__ out, long long out_ld, const T*
 
 // max_tokens_a_seq: the most tokens any sequence brings, if the host knows it (0: unknown); in the token-by-token kernel
 // it only chooses the chunk's size, which never shows in a result.
-// side_by_side: 1 lets steps of more than 4 tokens a sequence (heads of up to 256 rows) run in the kernel that forms a
-// chunk's outputs side by side: the same state to the last bit, outputs equal within 32-bit rounding (their terms are
-// added in another order), several times faster.  0 keeps every step in the token-by-token kernel, whose outputs do not
-// depend on how a sequence was cut into steps.
+// row_split >= 1 asks for the kernel that forms a chunk's outputs side by side (steps of more than 4 tokens a sequence):
+// the same state within 32-bit rounding of the activations, outputs equal within rounding (their terms are added in
+// another order), several times faster.  `out` then has row_split planes of `plane` elements, each CTA's share of the
+// outputs going to the plane of its rows (see lb_decay_row_split); the reader adds them.  0 keeps every step in the
+// token-by-token kernel, whose outputs do not depend on how a sequence was cut into steps.
+LB_EXPORT int lb_decay_row_split(int num_seqs, int heads, int dim, int vdim, int max_tokens_a_seq) {
+  if ((max_tokens_a_seq > 0 && max_tokens_a_seq <= 4) || dim > 1024) return 0;          // the token-by-token kernel
+  const long long base = (long long)num_seqs * heads * ((vdim + 31) / 32);
+  int r = 1;
+  while (r < 8 && base * r < 148 && dim / (2 * r) >= 32) r *= 2;     // fill the SMs, with 32 rows a CTA at least
+  while (dim / r > 256) r *= 2;                                      // at most 256 rows a CTA
+  return r;
+}
+
 LB_EXPORT int lb_decay_recurrence(const float* pre, long long ld, int q_col, int k_col, int v_col, const float* decay,
                                   float* state, float* out, const int* cu_tokens, const int* slots, int num_seqs,
-                                  int heads, int dim, int vdim, int max_tokens_a_seq, int side_by_side, cudaStream_t stream) {
+                                  int heads, int dim, int vdim, int max_tokens_a_seq, int row_split, long long plane,
+                                  cudaStream_t stream) {
   LB_CHECK_ARG(pre && decay && state && out && cu_tokens && slots, "decay_recurrence: null argument");
   LB_CHECK_ARG(num_seqs >= 0 && heads > 0 && heads <= 65535 && dim > 0 && dim <= 1024 && vdim > 0 && num_seqs <= 65535,
                "decay_recurrence: bad sizes seqs=%d heads=%d dim=%d vdim=%d (dim at most 1024)", num_seqs, heads, dim, vdim);
@@ -340,11 +375,16 @@ LB_EXPORT int lb_decay_recurrence(const float* pre, long long ld, int q_col, int
   p.state = state; p.out = out; p.cu_tokens = cu_tokens; p.slots = slots; p.heads = heads; p.dim = dim; p.vdim = vdim;
   const bool few = max_tokens_a_seq > 0 && max_tokens_a_seq <= 4;
   cudaError_t e;
-  if (side_by_side && !few && dim <= 256) {
-    if (dim <= 32) e = lb::launch_decay_chunk<4>(p, num_seqs, stream);
-    else if (dim <= 64) e = lb::launch_decay_chunk<8>(p, num_seqs, stream);
-    else if (dim <= 128) e = lb::launch_decay_chunk<16>(p, num_seqs, stream);
-    else e = lb::launch_decay_chunk<32>(p, num_seqs, stream);
+  if (row_split >= 1) {
+    lb::DecayChunkParams pc;
+    pc.b = p; pc.row_split = row_split; pc.plane = plane;
+    pc.rows_a_cta = ((dim + row_split - 1) / row_split + 3) / 4 * 4;
+    LB_CHECK_ARG(pc.rows_a_cta <= 256 && row_split <= 64, "decay_recurrence: %d rows cannot be shared out %d ways", dim, row_split);
+    const int rows = pc.rows_a_cta;
+    if (rows <= 32) e = lb::launch_decay_chunk<4>(pc, num_seqs, stream);
+    else if (rows <= 64) e = lb::launch_decay_chunk<8>(pc, num_seqs, stream);
+    else if (rows <= 128) e = lb::launch_decay_chunk<16>(pc, num_seqs, stream);
+    else e = lb::launch_decay_chunk<32>(pc, num_seqs, stream);
     if (e != cudaSuccess) { lb::set_error("decay_recurrence: %s", cudaGetErrorString(e)); return 2; }
     LB_CHECK_LAUNCH("decay_recurrence");
     return 0;
@@ -367,14 +407,15 @@ LB_EXPORT int lb_decay_recurrence(const float* pre, long long ld, int q_col, int
 
 LB_EXPORT int lb_rmsnorm_gated(void* out, int out_dtype, long long out_ld, const float* x, const float* weight,
                                const float* gate, long long gate_ld, float scale, float eps, int num_rows, int n,
-                               cudaStream_t stream) {
+                               int planes, long long plane, cudaStream_t stream) {
+  LB_CHECK_ARG(planes >= 1, "rmsnorm_gated: at least one plane");
   LB_CHECK_ARG(lb::valid_dtype(out_dtype) && out && x && weight && gate, "rmsnorm_gated: bad arguments");
   LB_CHECK_ARG(num_rows >= 0 && n > 0 && out_ld >= n && gate_ld >= n, "rmsnorm_gated: bad sizes rows=%d n=%d", num_rows, n);
   if (num_rows == 0) return 0;
   const int threads = n >= 2048 ? 512 : (n >= 512 ? 256 : 128);
   LB_DISPATCH_DTYPE(out_dtype, TO, {
     lb::launch(lb::rmsnorm_gated_kernel<TO>, dim3(num_rows), dim3(threads), 0, stream, (TO*)out, out_ld, x, weight, gate, gate_ld,
-               scale, eps, n);
+               scale, eps, n, planes, plane);
   })
   LB_CHECK_LAUNCH("rmsnorm_gated");
   return 0;

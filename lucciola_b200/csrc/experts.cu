@@ -232,15 +232,20 @@ __global__ void __launch_bounds__(256) expert_gemm_plain_kernel(ExpertGemmParams
 }
 
 // tensor cores (mma.sync m16n8k16), bfloat16 operands, 32-bit sums: a tile of 64 places x 128 output columns a CTA of
-// eight warps (warp w: rows (w & 1) * 32 .., columns (w >> 1) * 32 ..); K in blocks of 32 through two stages of shared
-// memory that 16-byte asynchronous copies fill while the tensor cores work on the other.  K a multiple of 8, 16-byte
-// aligned rows.
-constexpr int EM_BM = 64, EM_BN = 128, EM_BK = 32, EM_LD = EM_BK + 8, EM_STAGES = 2;
+// eight warps (warp w: rows (w & 1) * 32 .., columns (w >> 1) * 32 ..); K in blocks of 32 through four stages of shared
+// memory that 16-byte asynchronous copies fill three blocks ahead of the tensor cores (with a few tokens the kernel
+// streams the experts' weights, and the copies in flight are what fills the memory pipe); fragments by ldmatrix from
+// rows padded to 80 bytes.  K a multiple of 8, 16-byte aligned rows.
+constexpr int EM_BM = 64, EM_BN = 128, EM_BK = 32, EM_LD = EM_BK + 8, EM_STAGES = 4;
 
 __device__ __forceinline__ void ex_mma_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void ex_ldmatrix_x4(const void* addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"((uint32_t)__cvta_generic_to_shared(addr)));
 }
 __device__ __forceinline__ void ex_cp_async16(void* dst, const void* src, bool valid) {
   const int n = valid ? 16 : 0;             // 0: the 16 bytes are filled with zeros, nothing is read
@@ -294,43 +299,42 @@ __global__ void __launch_bounds__(256) expert_gemm_mma_kernel(ExpertGemmParams p
 #pragma unroll
       for (int k = 0; k < 4; ++k) { acc[i][j][k] = 0.f; if (GATED) acc2[i][j][k] = 0.f; }
   const int nk = (p.K + EM_BK - 1) / EM_BK;
-  load_stage(0, 0);
-  asm volatile("cp.async.commit_group;" ::: "memory");
-  for (int kb = 0; kb < nk; ++kb) {
-    const int st = kb & 1;
-    if (kb + 1 < nk) load_stage(st ^ 1, (kb + 1) * EM_BK);
+#pragma unroll
+  for (int st = 0; st < EM_STAGES - 1; ++st) {
+    if (st < nk) load_stage(st, st * EM_BK);
     asm volatile("cp.async.commit_group;" ::: "memory");
-    asm volatile("cp.async.wait_group 1;" ::: "memory");            // block kb has landed (the group after it may be in flight)
-    __syncthreads();
+  }
+  // ldmatrix addresses of this lane: A rows (lane & 7) + 8 * ((lane >> 3) & 1), k half (lane >> 4); B rows (lane & 7) + 8 * (lane >> 4),
+  // k half (lane >> 3) & 1
+  const int a_lr = (lane & 7) + ((lane >> 3) & 1) * 8, a_lk = (lane >> 4) * 8;
+  const int b_lr = (lane & 7) + (lane >> 4) * 8, b_lk = ((lane >> 3) & 1) * 8;
+  for (int kb = 0; kb < nk; ++kb) {
+    const int st = kb % EM_STAGES;
+    asm volatile("cp.async.wait_group %0;" ::"n"(EM_STAGES - 2) : "memory");   // block kb has landed
+    __syncthreads();                                                           // and the stage of block kb - 1 is free
+    if (kb + EM_STAGES - 1 < nk) load_stage((kb + EM_STAGES - 1) % EM_STAGES, (kb + EM_STAGES - 1) * EM_BK);
+    asm volatile("cp.async.commit_group;" ::: "memory");
 #pragma unroll
     for (int kk = 0; kk < EM_BK; kk += 16) {
       uint32_t a[2][4];
 #pragma unroll
-      for (int mi = 0; mi < 2; ++mi) {
-        const bf16* ar = As + (st * EM_BM + wm + mi * 16 + g) * EM_LD + kk + 2 * t4;
-        a[mi][0] = *reinterpret_cast<const uint32_t*>(ar);
-        a[mi][1] = *reinterpret_cast<const uint32_t*>(ar + 8 * EM_LD);
-        a[mi][2] = *reinterpret_cast<const uint32_t*>(ar + 8);
-        a[mi][3] = *reinterpret_cast<const uint32_t*>(ar + 8 * EM_LD + 8);
-      }
+      for (int mi = 0; mi < 2; ++mi)
+        ex_ldmatrix_x4(As + (st * EM_BM + wm + mi * 16 + a_lr) * EM_LD + kk + a_lk, a[mi][0], a[mi][1], a[mi][2], a[mi][3]);
 #pragma unroll
-      for (int nb = 0; nb < 4; ++nb) {
-        uint32_t bb[2];
-        const bf16* br = Bs + ((st * NB + 0) * EM_BN + wn + nb * 8 + g) * EM_LD + kk + 2 * t4;
-        bb[0] = *reinterpret_cast<const uint32_t*>(br);
-        bb[1] = *reinterpret_cast<const uint32_t*>(br + 8);
-        ex_mma_16816(acc[0][nb], a[0], bb);
-        ex_mma_16816(acc[1][nb], a[1], bb);
+      for (int nb = 0; nb < 4; nb += 2) {
+        uint32_t b0, b1, b2, b3;
+        ex_ldmatrix_x4(Bs + ((st * NB + 0) * EM_BN + wn + nb * 8 + b_lr) * EM_LD + kk + b_lk, b0, b1, b2, b3);
+        const uint32_t lo[2] = {b0, b1}, hi[2] = {b2, b3};
+        ex_mma_16816(acc[0][nb], a[0], lo); ex_mma_16816(acc[1][nb], a[1], lo);
+        ex_mma_16816(acc[0][nb + 1], a[0], hi); ex_mma_16816(acc[1][nb + 1], a[1], hi);
         if (GATED) {
-          const bf16* br2 = Bs + ((st * NB + 1) * EM_BN + wn + nb * 8 + g) * EM_LD + kk + 2 * t4;
-          bb[0] = *reinterpret_cast<const uint32_t*>(br2);
-          bb[1] = *reinterpret_cast<const uint32_t*>(br2 + 8);
-          ex_mma_16816(acc2[0][nb], a[0], bb);
-          ex_mma_16816(acc2[1][nb], a[1], bb);
+          ex_ldmatrix_x4(Bs + ((st * NB + 1) * EM_BN + wn + nb * 8 + b_lr) * EM_LD + kk + b_lk, b0, b1, b2, b3);
+          const uint32_t lo2[2] = {b0, b1}, hi2[2] = {b2, b3};
+          ex_mma_16816(acc2[0][nb], a[0], lo2); ex_mma_16816(acc2[1][nb], a[1], lo2);
+          ex_mma_16816(acc2[0][nb + 1], a[0], hi2); ex_mma_16816(acc2[1][nb + 1], a[1], hi2);
         }
       }
     }
-    __syncthreads();                                                // the stage may be filled again
   }
   TY* y = (TY*)p.y;
 #pragma unroll
@@ -419,9 +423,11 @@ LB_EXPORT int lb_expert_gemm(void* y, int y_dtype, const void* x, int x_dtype, c
   if (mma) {
     dim3 grid((ncols + lb::EM_BN - 1) / lb::EM_BN, max_tiles);
     static bool attr_set = false;
-    if (!attr_set) {       // the gated kernel's two stages need more shared memory than a launch gets unasked
+    if (!attr_set) {       // the stages need more shared memory than a launch gets unasked
       cudaFuncSetAttribute(lb::expert_gemm_mma_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::expert_mma_smem<true>());
       cudaFuncSetAttribute(lb::expert_gemm_mma_kernel<lb::bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::expert_mma_smem<true>());
+      cudaFuncSetAttribute(lb::expert_gemm_mma_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::expert_mma_smem<false>());
+      cudaFuncSetAttribute(lb::expert_gemm_mma_kernel<lb::bf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::expert_mma_smem<false>());
       attr_set = true;
     }
     LB_DISPATCH_DTYPE(y_dtype, TY, {

@@ -36,9 +36,9 @@ _SIGNATURES = {
                          c_int, c_int, c_void_p],
     "lb_round_copy": [c_void_p, c_int, c_void_p, c_longlong, c_void_p],
     "lb_decay_recurrence": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                            c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                            c_int, c_int, c_int, c_int, c_int, c_int, c_longlong, c_void_p],
     "lb_rmsnorm_gated": [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_longlong, c_float, c_float, c_int, c_int,
-                         c_void_p],
+                         c_int, c_longlong, c_void_p],
     "lb_head_gate": [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_longlong, c_float, c_int, c_int, c_int, c_void_p],
     "lb_route_topk": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "lb_expert_dispatch": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
@@ -543,33 +543,48 @@ def round_copy(out: torch.Tensor, x: torch.Tensor, stream: int) -> None:
     _call("lb_round_copy", out.data_ptr(), dtype_code(out.dtype), x.data_ptr(), x.numel(), stream)
 
 
+def decay_row_split(num_seqs: int, heads: int, dim: int, vdim: int, max_tokens_a_seq: int) -> int:
+    """Into how many shares of rows the kernel that forms outputs side by side cuts a head's state for a step of this
+    shape (0: the step runs token by token): as many as fill the SMs, with 32 to 256 rows a share."""
+    lib = library()
+    lib.lb_decay_row_split.argtypes = [c_int, c_int, c_int, c_int, c_int]
+    lib.lb_decay_row_split.restype = c_int
+    return int(lib.lb_decay_row_split(num_seqs, heads, dim, vdim, max_tokens_a_seq))
+
+
 def decay_recurrence(pre: torch.Tensor, q_col: int, k_col: int, v_col: int, decay: torch.Tensor, state: torch.Tensor,
                      out: torch.Tensor, step, heads: int, dim: int, vdim: int, stream: int, max_tokens_a_seq: int = 0,
-                     side_by_side: bool = False) -> None:
+                     row_split: int = 0) -> None:
     """Linear attention with a fixed decay per head over this step's tokens: S <- decay_h S + k v^T, out = S^T q with
     q, k, v = silu of the columns of `pre` (float32, row-strided) at q_col, k_col, v_col; state [slots + 1, heads, dim, vdim]
     float32 is read and written at each sequence's slot; out [T, heads * vdim] float32.
-    `side_by_side`: steps of more than 4 tokens a sequence may form the outputs of 16 tokens at a time from the state
-    before them and the tokens' own scores (32-bit, the same state, outputs equal within rounding, several times faster);
-    without it every output's sum has one order however the sequence is cut."""
+    `row_split` >= 1 (see decay_row_split): the outputs of 16 tokens at a time are formed from the state before them
+    and the tokens' own scores (32-bit, outputs equal within rounding, several times faster), the state's rows shared out
+    over row_split CTAs; out is then [row_split, T, heads * vdim] and the sum over its first dimension is meant.
+    With 0 every output's sum has one order however the sequence is cut."""
     _check(decay, "decay", torch.float32); _check(state, "recurrent state", torch.float32); _check(out, "recurrence output", torch.float32)
     if pre.dtype != torch.float32 or pre.stride(1) != 1 or not pre.is_cuda:
         raise KernelError("the input projections must be float32 on the GPU with unit column stride")
+    T = pre.shape[0]
+    if tuple(out.shape) != ((row_split, T, heads * vdim) if row_split >= 1 else (T, heads * vdim)):
+        raise KernelError(f"the recurrence's output has the wrong shape {tuple(out.shape)}")
     _call("lb_decay_recurrence", pre.data_ptr(), pre.stride(0), q_col, k_col, v_col, decay.data_ptr(), state.data_ptr(),
           out.data_ptr(), step.cu_tokens.data_ptr(), step.state_slots.data_ptr(), step.num_seqs, heads, dim, vdim,
-          max_tokens_a_seq, 1 if side_by_side else 0, stream)
+          max_tokens_a_seq, row_split, T * heads * vdim, stream)
 
 
 def rmsnorm_gated(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, gate: torch.Tensor, scale: float, eps: float,
                   stream: int) -> None:
-    """out = x * rsqrt(mean(x^2) + eps) * weight * sigmoid(gate) * scale, row by row; x float32 [T, n] contiguous, gate
-    float32 and out (any type) may be column ranges of wider matrices."""
+    """out = x * rsqrt(mean(x^2) + eps) * weight * sigmoid(gate) * scale, row by row; x float32 [T, n] contiguous (or
+    [planes, T, n], whose sum over the planes is meant), gate float32 and out (any type) may be column ranges of wider
+    matrices."""
     _check(x, "norm input", torch.float32); _check(weight, "norm weight", torch.float32)
-    T, n = x.shape
+    planes = x.shape[0] if x.dim() == 3 else 1
+    T, n = x.shape[-2], x.shape[-1]
     if gate.dtype != torch.float32 or gate.stride(1) != 1 or out.stride(1) != 1 or tuple(gate.shape) != (T, n) or tuple(out.shape) != (T, n):
         raise KernelError("gate (float32) and out must be [T, n] views with unit column stride")
     _call("lb_rmsnorm_gated", out.data_ptr(), dtype_code(out.dtype), out.stride(0) if T > 1 else n, x.data_ptr(), weight.data_ptr(),
-          gate.data_ptr(), gate.stride(0) if T > 1 else n, scale, eps, T, n, stream)
+          gate.data_ptr(), gate.stride(0) if T > 1 else n, scale, eps, T, n, planes, T * n, stream)
 
 
 def head_gate(out: torch.Tensor, x: torch.Tensor, gate: torch.Tensor, scale: float, stream: int) -> None:

@@ -72,9 +72,11 @@ class DecayLinearAttention(Mixer):
             raise ops.KernelError("a recurrent mixer has no cache another call could have written")
         rt, n = self.rt, self.heads * self.dim
         T = pre.shape[0]
-        o = rt.empty((T, self.inner_size), torch.float32)
+        # the bfloat16 engine forms the outputs of long steps 16 tokens at a time, the rows of the state shared out over CTAs
+        split = ops.decay_row_split(step.num_seqs, self.heads, self.dim, self.vdim, step.max_q_len) if rt.fast_kernels else 0
+        o = rt.empty((split, T, self.inner_size) if split else (T, self.inner_size), torch.float32)
         ops.decay_recurrence(pre, 0, n, 2 * n, self.decay, cache.state, o, step, self.heads, self.dim, self.vdim, rt.stream,
-                             max_tokens_a_seq=step.max_q_len, side_by_side=rt.fast_kernels)
+                             max_tokens_a_seq=step.max_q_len, row_split=split)
         g0 = 2 * n + self.inner_size
         ops.rmsnorm_gated(out, o, self.norm_w, pre[:, g0:g0 + self.inner_size], out_scale, self.eps, rt.stream)
 
