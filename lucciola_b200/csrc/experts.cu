@@ -132,6 +132,52 @@ __global__ void expert_dispatch_kernel(const int* __restrict__ ids, int pairs, i
   }
 }
 
+// The same sort with every expert's run padded to whole tiles of `tile` places, for products that take their rows
+// from a matrix by whole tiles (the tensor-memory product): place_of [pairs], pair_at [places] (-1 where a place is
+// padding), tile_group [places / tile] (the expert of each tile; the tiles behind the last run name expert 0 and hold padding).
+__global__ void expert_dispatch_padded_kernel(const int* __restrict__ ids, int pairs, int experts, int tile, int places,
+                                              int* __restrict__ pair_at, int* __restrict__ place_of, int* __restrict__ tile_group) {
+  extern __shared__ int ism[];
+  pdl_trigger();
+  pdl_wait();
+  int* count = ism;                 // [experts]
+  int* start = ism + experts;       // [experts + 1]
+  for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+  for (int i = threadIdx.x; i < places; i += blockDim.x) pair_at[i] = -1;
+  for (int i = threadIdx.x; i < places / tile; i += blockDim.x) tile_group[i] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) place_of[i] = atomicAdd(&count[ids[i]], 1);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int a = 0;
+    for (int e = 0; e < experts; ++e) { start[e] = a; a += (count[e] + tile - 1) / tile * tile; }
+    start[experts] = a;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int place = start[ids[i]] + place_of[i];
+    place_of[i] = place;
+    pair_at[place] = i;
+  }
+  for (int e = threadIdx.x; e < experts; e += blockDim.x)
+    for (int t = start[e] / tile; t < start[e + 1] / tile; ++t) tile_group[t] = e;
+}
+
+// xs[place, :] = x[pair_at[place] / top, :] (zeros where the place is padding), 16 bytes a thread
+__global__ void expert_gather_rows_kernel(uint4* __restrict__ xs, const uint4* __restrict__ x, const int* __restrict__ pair_at,
+                                          int top, int row_words) {
+  pdl_trigger();
+  pdl_wait();
+  const int place = blockIdx.x, pair = pair_at[place];
+  uint4* dst = xs + (size_t)place * row_words;
+  if (pair < 0) {
+    for (int i = threadIdx.x; i < row_words; i += blockDim.x) dst[i] = make_uint4(0u, 0u, 0u, 0u);
+    return;
+  }
+  const uint4* src = x + (size_t)(pair / top) * row_words;
+  for (int i = threadIdx.x; i < row_words; i += blockDim.x) dst[i] = src[i];
+}
+
 // ---- product ---------------------------------------------------------------------------------------------------
 __device__ __forceinline__ float expert_act(int act, float limit, float g, float u) {
   if (act == 1) return fmaxf(g, 0.f) * u;
@@ -152,7 +198,14 @@ struct ExpertGemmParams {
   long long ldx, ldy;
   int gather;               // 1: x row of a place = pair_at[place] / top; 0: the place
   int gated, act; float limit;
+  int interleaved;          // gated only: gate and up rows alternate in blocks of 64 (gate rows of 64 features, then their up rows)
 };
+
+// rows of W[e] that hold the gate and the up weights of output column n
+__device__ __forceinline__ void gate_up_rows(const ExpertGemmParams& p, int n, int ncols, int& gate_row, int& up_row) {
+  if (p.interleaved) { gate_row = (n >> 6) * 128 + (n & 63); up_row = gate_row + 64; }
+  else { gate_row = n; up_row = ncols + n; }
+}
 
 // ordinary pipes, any types: a tile of 64 places x 64 output columns, k in increasing order by one thread an element
 template <typename TX, typename TW, typename TY, bool GATED>
@@ -195,8 +248,10 @@ __global__ void __launch_bounds__(256) expert_gemm_plain_kernel(ExpertGemmParams
       const int r = idx / EX_BK, c = idx % EX_BK;
       const int gn = n0 + r, gk = k0 + c;
       const bool ok = gn < ncols && gk < p.K;
-      ws[0][c][r] = ok ? to_f32(w[(size_t)gn * p.K + gk]) : 0.f;
-      if (GATED) ws[1][c][r] = ok ? to_f32(w[(size_t)(ncols + gn) * p.K + gk]) : 0.f;
+      int gr = gn, ur = gn;
+      if (GATED) gate_up_rows(p, gn, ncols, gr, ur);
+      ws[0][c][r] = ok ? to_f32(w[(size_t)gr * p.K + gk]) : 0.f;
+      if (GATED) ws[1][c][r] = ok ? to_f32(w[(size_t)ur * p.K + gk]) : 0.f;
     }
     __syncthreads();
 #pragma unroll
@@ -287,8 +342,10 @@ __global__ void __launch_bounds__(256) expert_gemm_mma_kernel(ExpertGemmParams p
     for (int it = 0; it < 2; ++it) {
       const int idx = tid + it * 256, r = idx >> 2, c = (idx & 3) * 8;   // 128 rows x 4 pieces
       const bool ok = n0 + r < ncols && k0 + c < p.K;
-      ex_cp_async16(Bs + ((st * NB + 0) * EM_BN + r) * EM_LD + c, ok ? w + (size_t)(n0 + r) * p.K + k0 + c : w, ok);
-      if (GATED) ex_cp_async16(Bs + ((st * NB + 1) * EM_BN + r) * EM_LD + c, ok ? w + (size_t)(ncols + n0 + r) * p.K + k0 + c : w, ok);
+      int gr = n0 + r, ur = n0 + r;
+      if (GATED) gate_up_rows(p, n0 + r, ncols, gr, ur);
+      ex_cp_async16(Bs + ((st * NB + 0) * EM_BN + r) * EM_LD + c, ok ? w + (size_t)gr * p.K + k0 + c : w, ok);
+      if (GATED) ex_cp_async16(Bs + ((st * NB + 1) * EM_BN + r) * EM_LD + c, ok ? w + (size_t)ur * p.K + k0 + c : w, ok);
     }
   };
   float acc[2][4][4], acc2[GATED ? 2 : 1][4][4];
@@ -404,11 +461,34 @@ LB_EXPORT int lb_expert_dispatch(const int* ids, int pairs, int experts, int* of
   return 0;
 }
 
+// places: a multiple of tile, at least pairs + experts * (tile - 1) rounded up to it
+LB_EXPORT int lb_expert_dispatch_padded(const int* ids, int pairs, int experts, int tile, int places, int* pair_at, int* place_of,
+                                        int* tile_group, cudaStream_t stream) {
+  LB_CHECK_ARG(ids && pair_at && place_of && tile_group, "expert_dispatch_padded: null argument");
+  LB_CHECK_ARG(pairs >= 0 && experts > 0 && experts <= 4096 && tile > 0 && places % tile == 0 && places >= pairs + experts * (tile - 1),
+               "expert_dispatch_padded: bad sizes pairs=%d experts=%d tile=%d places=%d", pairs, experts, tile, places);
+  lb::launch(lb::expert_dispatch_padded_kernel, dim3(1), dim3(1024), (size_t)(2 * experts + 1) * sizeof(int), stream, ids, pairs, experts,
+             tile, places, pair_at, place_of, tile_group);
+  LB_CHECK_LAUNCH("expert_dispatch_padded");
+  return 0;
+}
+
+// xs [places, width] = the rows of x [T, width] (2-byte elements, width a multiple of 8) that the places name
+LB_EXPORT int lb_expert_gather_rows(void* xs, const void* x, const int* pair_at, int places, int top, int width, cudaStream_t stream) {
+  LB_CHECK_ARG(xs && x && pair_at && places >= 0 && top > 0 && width > 0 && width % 8 == 0 && (uintptr_t)xs % 16 == 0 && (uintptr_t)x % 16 == 0,
+               "expert_gather_rows: bad arguments");
+  if (places == 0) return 0;
+  lb::launch(lb::expert_gather_rows_kernel, dim3(places), dim3(128), 0, stream, (uint4*)xs, (const uint4*)x, pair_at, top, width / 8);
+  LB_CHECK_LAUNCH("expert_gather_rows");
+  return 0;
+}
+
 // y[place, :] = act(x[row(place)] . W[e]^T) over the row tiles of `meta`; max_tiles bounds their number (the grid).
 // fast: 1 allows the tensor-core kernel (bfloat16 x and W, K a multiple of 8, 16-byte aligned rows).
 LB_EXPORT int lb_expert_gemm(void* y, int y_dtype, const void* x, int x_dtype, const void* w, int w_dtype, const int* meta,
                              const int* pair_at, int max_tiles, int N, int K, long long ldx, long long ldy, int top, int gather,
-                             int gated, int act, float limit, int fast, cudaStream_t stream) {
+                             int gated, int act, float limit, int fast, int interleaved, cudaStream_t stream) {
+  LB_CHECK_ARG(!interleaved || (gated && N % 128 == 0), "expert_gemm: interleaved gate and up rows come in blocks of 64");
   LB_CHECK_ARG(lb::valid_dtype(y_dtype) && lb::valid_dtype(x_dtype) && lb::valid_dtype(w_dtype), "expert_gemm: bad dtype");
   LB_CHECK_ARG(y && x && w && meta && pair_at && N > 0 && K > 0 && top > 0 && max_tiles >= 0 && (!gated || N % 2 == 0) && ldx >= K,
                "expert_gemm: bad arguments N=%d K=%d", N, K);
@@ -417,7 +497,7 @@ LB_EXPORT int lb_expert_gemm(void* y, int y_dtype, const void* x, int x_dtype, c
   if (max_tiles == 0) return 0;
   lb::ExpertGemmParams p;
   p.y = y; p.x = x; p.w = w; p.meta = meta; p.pair_at = pair_at; p.N = N; p.K = K; p.top = top; p.ldx = ldx; p.ldy = ldy;
-  p.gather = gather; p.gated = gated; p.act = act; p.limit = limit;
+  p.gather = gather; p.gated = gated; p.act = act; p.limit = limit; p.interleaved = interleaved;
   const int ncols = gated ? N / 2 : N;
   const bool mma = fast && x_dtype == LB_BF16 && w_dtype == LB_BF16 && K % 8 == 0 && ldx % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0;
   if (mma) {

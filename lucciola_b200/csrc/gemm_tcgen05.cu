@@ -269,6 +269,9 @@ struct GemmParams {
                         // features; the output has N/2 columns and holds act(gate) * up (computed in 32-bit) with
                         // act = silu (1), relu (2), the tanh form of gelu (3) or the clamped swish (4, see gated_mul)
   float act_limit = 0.f; // the clamp of activation 4
+  const int* tile_group = nullptr;   // many-token kernel only: w holds several matrices of N rows one below the other, and token
+                                     // tile i (128 tokens) is multiplied with matrix tile_group[i] (tokens sorted into runs by
+                                     // group, each run padded to whole tiles: the experts of a routed feed-forward)
   unsigned long long wait_cycles = WAIT_CYCLES;   // after this many clock cycles a wait on a barrier gives up
   int skip_loads = 0;   // tests of the give-up path only: the producer requests nothing, so the first wait runs out
 };
@@ -863,7 +866,10 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
   };
   // bytes a stage's barrier expects (of a pair: both CTAs' bytes on the first CTA's barrier), the first weight row this CTA loads
   auto stage_bytes = [&](int bn) { return (uint32_t)(PAIR ? 2 * (L::A_BYTES + (bn / 2) * BK * 2) : L::A_BYTES + bn * BK * 2); };
-  auto w_row = [&](int n0, int bn) { return PAIR ? n0 + (int)rank * (bn / 2) : n0; };
+  auto w_row = [&](int n0, int bn, int m0) {
+    const int group_row = p.tile_group ? p.tile_group[m0 / PF_BM] * p.N : 0;     // (read behind pdl_wait: a kernel of the step writes it)
+    return group_row + (PAIR ? n0 + (int)rank * (bn / 2) : n0);
+  };
   auto load = [&](uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
     if (PAIR) tma_load_2d_pair(dst, map, x, y, map_to_rank(bar, 0));
     else tma_load_2d(dst, map, x, y, bar);
@@ -901,13 +907,13 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
       long long it = 0;                       // stage uses so far
       bool ok = true;
       // The weights of the first tile do not depend on the kernel before this one.
-      const int early = num_kb < PF_STAGES ? num_kb : PF_STAGES;
+      const int early = p.tile_group ? 0 : (num_kb < PF_STAGES ? num_kb : PF_STAGES);   // (which weights: known behind the wait only)
       {
         int m0, n0, bn;
         const CUtensorMap* mw = tile_of(slot_id, m0, n0, bn) ? &map_w2 : &map_w;
         for (int i = 0; i < early; ++i) {
           if (rank == 0) mbar_expect_tx(full_bar(i), stage_bytes(bn));
-          load(smem_base + i * L::STAGE_BYTES + L::A_BYTES, mw, i * BK, w_row(n0, bn), full_bar(i));
+          load(smem_base + i * L::STAGE_BYTES + L::A_BYTES, mw, i * BK, w_row(n0, bn, m0), full_bar(i));
         }
         pdl_wait();
         for (int i = 0; i < early; ++i)
@@ -925,7 +931,7 @@ gemm_tcgen05_prefill_kernel(const __grid_constant__ CUtensorMap map_x, const __g
           if (rank == 0) mbar_expect_tx(full_bar(s), stage_tx);
           const uint32_t dst = smem_base + s * L::STAGE_BYTES;
           load(dst, &map_x, kb * BK, m0, full_bar(s));
-          load(dst + L::A_BYTES, mw, kb * BK, w_row(n0, bn), full_bar(s));
+          load(dst + L::A_BYTES, mw, kb * BK, w_row(n0, bn, m0), full_bar(s));
           it = use + 1;
         }
         if (t == 0 && it < early) it = early;
@@ -1302,19 +1308,22 @@ static int prefill_feature_tiles(const PrefillPlan& plan, int N) {
 
 static int launch_prefill(const void* y, int y_dtype, const void* x, const void* w, int M, int N, int K, long long ldx,
                           long long ldy, int swiglu, int force_bn, int pair, cudaStream_t stream,
-                          const AddNormEpilogue* an = nullptr, const RowScale* rs = nullptr, float act_limit = 0.f) {
+                          const AddNormEpilogue* an = nullptr, const RowScale* rs = nullptr, float act_limit = 0.f,
+                          const int* tile_group = nullptr, int groups = 1) {
   bool use_pair; int m_tiles, slots; PrefillPlan plan;
+  if (tile_group) pair = 1;               // a group's run of tokens is padded to tiles of 128, not to pairs of them
   prefill_choose(M, N, K, swiglu, force_bn, pair, &use_pair, &m_tiles, &slots, &plan);
   if (use_pair && (plan.bn1 % 32 || plan.bn2 % 32)) { set_error("gemm_tcgen05: pairs of CTAs take tile widths that are multiples of 32"); return 1; }
   const int box1 = use_pair ? plan.bn1 / 2 : plan.bn1, box2 = use_pair ? plan.bn2 / 2 : plan.bn2;
   CUtensorMap mx, mw, mw2;
-  if (!cached_map(&mx, x, M, K, ldx, PF_BM) || !cached_map(&mw, w, N, K, K, box1) || !cached_map(&mw2, w, N, K, K, box2)) {
+  const long long w_rows = (long long)N * (tile_group ? groups : 1);
+  if (!cached_map(&mx, x, M, K, ldx, PF_BM) || !cached_map(&mw, w, w_rows, K, K, box1) || !cached_map(&mw2, w, w_rows, K, K, box2)) {
     set_error("gemm_tcgen05: cuTensorMapEncodeTiled failed (M=%d N=%d K=%d ldx=%lld)", M, N, K, ldx);
     return 3;
   }
   GemmParams p;
   p.y = const_cast<void*>(y); p.workspace = nullptr; p.counters = nullptr; p.M = M; p.N = N; p.K = K; p.ldy = ldy;
-  p.out_dtype = y_dtype; p.cluster = 0; p.swiglu = swiglu; p.act_limit = act_limit;
+  p.out_dtype = y_dtype; p.cluster = 0; p.swiglu = swiglu; p.act_limit = act_limit; p.tile_group = tile_group;
   if (an) {
     p.an = *an; p.an.on = 1;
     if (p.an.tiles != prefill_feature_tiles(plan, N)) { set_error("gemm_tcgen05: %d columns of partial sums, the plan has %d feature tiles", p.an.tiles, prefill_feature_tiles(plan, N)); return 1; }
@@ -1372,6 +1381,25 @@ LB_EXPORT int lb_gemm_tcgen05_pair_slots() { return lb::g_pair_slots_seen; }
 LB_EXPORT void lb_gemm_tcgen05_prefill_plan(int M, int N, int swiglu, int num_sms, int* out) {
   const lb::PrefillPlan pl = lb::prefill_plan((M + lb::PF_BM - 1) / lb::PF_BM, N, swiglu ? 128 : 16, num_sms > 0 ? num_sms : 148);
   out[0] = pl.cols1; out[1] = pl.bn1; out[2] = pl.bn2;
+}
+
+// y[m, :] = act(x[m, :] . W[g(m)]^T) for `groups` matrices of N rows stacked in w ([groups * N, K]), with g(m) =
+// tile_group[m / 128] (int32 on the device, one entry for every 128 rows of x: the rows are sorted into runs by group and
+// each run is padded to whole tiles; rows that belong to no group compute something nobody reads).  The many-token
+// kernel with one more term in the weights' coordinate; swiglu and act_limit as in lb_gemm_tcgen05.
+LB_EXPORT int lb_gemm_tcgen05_grouped(void* y, int y_dtype, const void* x, const void* w, int M, int N, int K, long long ldx,
+                                      long long ldy, int swiglu, float act_limit, const int* tile_group, int groups,
+                                      cudaStream_t stream) {
+  LB_CHECK_ARG(lb::valid_dtype(y_dtype) && tile_group && groups > 0, "gemm_tcgen05_grouped: bad arguments");
+  LB_CHECK_ARG(M >= 0 && N > 0 && K > 0 && ldx >= K && ldy >= (swiglu ? N / 2 : N), "gemm_tcgen05_grouped: bad sizes M=%d N=%d K=%d", M, N, K);
+  LB_CHECK_ARG(!swiglu || N % 128 == 0, "gemm_tcgen05_grouped: the fused activation needs gate and up rows in blocks of 64 (N=%d)", N);
+  LB_CHECK_ARG(K % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0),
+               "gemm_tcgen05_grouped: K and the row stride must be multiples of 8, the operands 16-byte aligned");
+  LB_CHECK_ARG((long long)N * groups < (1ll << 31), "gemm_tcgen05_grouped: too many weight rows");
+  if (M == 0) return 0;
+  if (int rc = lb::launch_prefill(y, y_dtype, x, w, M, N, K, ldx, ldy, swiglu, 0, 1, stream, nullptr, nullptr, act_limit, tile_group, groups)) return rc;
+  LB_CHECK_LAUNCH("gemm_tcgen05_grouped");
+  return 0;
 }
 
 // Which (token tile, splits) the launcher would choose; exposed so that callers can size the workspace

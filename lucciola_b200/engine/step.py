@@ -127,8 +127,8 @@ class ModelRunner:
                 raise RuntimeError("no memory left for cache pages")
         self.num_pages = int(num_pages)
         # A model whose positions have no limit of their own (max_positions 0) takes the option, or else what all pages
-        # together hold: the block tables of a step are as wide as the longest sequence allowed.
-        positions = model.max_positions or options.max_model_len or self.num_pages * self.page_size
+        # together hold, up to 128 K tokens: the block tables of a step are as wide as the longest sequence allowed.
+        positions = model.max_positions or options.max_model_len or min(self.num_pages * self.page_size, 1 << 17)
         self.max_model_len = options.max_model_len or positions
         if self.max_model_len > positions:
             raise ValueError(f"max_model_len {self.max_model_len} exceeds the model's {positions} positions")

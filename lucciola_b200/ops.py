@@ -43,7 +43,11 @@ _SIGNATURES = {
     "lb_route_topk": [c_void_p, c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "lb_expert_dispatch": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     "lb_expert_gemm": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong,
-                       c_longlong, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+                       c_longlong, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p],
+    "lb_expert_dispatch_padded": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+    "lb_expert_gather_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "lb_gemm_tcgen05_grouped": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_longlong, c_longlong, c_int, c_float,
+                                c_void_p, c_int, c_void_p],
     "lb_expert_combine": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
     "lb_add_group_rmsnorm": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                              c_float, c_void_p],
@@ -639,10 +643,12 @@ def expert_dispatch(ids: torch.Tensor, experts: int, offsets: torch.Tensor, pair
 
 
 def expert_gemm(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, meta: torch.Tensor, pair_at: torch.Tensor, top: int,
-                gather: bool, stream: int, act: str | None = None, limit: float = 0.0, fast: bool = True) -> None:
+                gather: bool, stream: int, act: str | None = None, limit: float = 0.0, fast: bool = True,
+                interleaved: bool = False) -> None:
     """y[place] = x[row(place)] . w[e]^T for the places of every expert e (see expert_dispatch); w [experts, N, K].
-    `gather`: row(place) is the pair's token, else the place.  With `act`, w[e] is N/2 gate rows then N/2 up rows and
-    y[place] = act(gate) * up with N/2 columns."""
+    `gather`: row(place) is the pair's token, else the place.  With `act`, w[e] is N/2 gate rows then N/2 up rows (or,
+    `interleaved`, blocks of 64 gate rows and their 64 up rows in turn, see interleave_gate_up) and y[place] =
+    act(gate) * up with N/2 columns."""
     _check(y, "expert output"); _check(x, "expert input"); _check(w, "expert weights")
     E, N, K = w.shape
     pairs = pair_at.numel()
@@ -651,7 +657,50 @@ def expert_gemm(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, meta: torch.T
         raise KernelError(f"expert_gemm shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
     _call("lb_expert_gemm", y.data_ptr(), dtype_code(y.dtype), x.data_ptr(), dtype_code(x.dtype), w.data_ptr(), dtype_code(w.dtype),
           meta.data_ptr(), pair_at.data_ptr(), expert_max_tiles(pairs, E), N, K, K, cols, top, 1 if gather else 0,
-          1 if act is not None else 0, GATE_ACTS[act] if act is not None else 0, limit, 1 if fast else 0, stream)
+          1 if act is not None else 0, GATE_ACTS[act] if act is not None else 0, limit, 1 if fast else 0, 1 if interleaved else 0, stream)
+
+
+GROUP_TILE = 128          # token tile of the grouped tensor-memory product
+
+
+def expert_padded_places(pairs: int, experts: int) -> int:
+    """Places the pairs of token and choice take when every expert's run is padded to whole tiles of GROUP_TILE."""
+    return -(-(pairs + experts * (GROUP_TILE - 1)) // GROUP_TILE) * GROUP_TILE
+
+
+def expert_dispatch_padded(ids: torch.Tensor, experts: int, pair_at: torch.Tensor, place_of: torch.Tensor, tile_group: torch.Tensor,
+                           stream: int) -> None:
+    """Sort the pairs by expert with every run padded to whole tiles: pair_at [places] (-1: padding), place_of [pairs],
+    tile_group [places / GROUP_TILE] (the expert of each tile), places = expert_padded_places(pairs, experts)."""
+    for t, what in ((ids, "expert ids"), (pair_at, "pair list"), (place_of, "places"), (tile_group, "tile list")):
+        _check(t, what, torch.int32)
+    pairs, places = ids.numel(), pair_at.numel()
+    if places != expert_padded_places(pairs, experts) or place_of.numel() < pairs or tile_group.numel() < places // GROUP_TILE:
+        raise KernelError("expert_dispatch_padded: an output has the wrong size")
+    _call("lb_expert_dispatch_padded", ids.data_ptr(), pairs, experts, GROUP_TILE, places, pair_at.data_ptr(), place_of.data_ptr(),
+          tile_group.data_ptr(), stream)
+
+
+def expert_gather_rows(xs: torch.Tensor, x: torch.Tensor, pair_at: torch.Tensor, top: int, stream: int) -> None:
+    """xs[place] = x[pair_at[place] // top] (zeros where the place is padding); bfloat16 rows of a multiple of 8 values."""
+    _check(xs, "gathered rows", torch.bfloat16); _check(x, "rows", torch.bfloat16); _check(pair_at, "pair list", torch.int32)
+    if xs.shape[0] != pair_at.numel() or xs.shape[1] != x.shape[1]:
+        raise KernelError("expert_gather_rows: shapes do not fit")
+    _call("lb_expert_gather_rows", xs.data_ptr(), x.data_ptr(), pair_at.data_ptr(), xs.shape[0], top, x.shape[1], stream)
+
+
+def gemm_tcgen05_grouped(y: torch.Tensor, x: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, stream: int,
+                         act: str | None = None, limit: float = 0.0) -> None:
+    """y[m] = x[m] . w[g]^T with g = tile_group[m // GROUP_TILE], on the tensor cores (the many-token kernel of gemm_tcgen05);
+    w [groups, N, K] bfloat16.  With `act`, w[g] holds gate and up rows interleaved in blocks of 64 and y = act(gate) * up."""
+    _check(y, "y"); _check(x, "x", torch.bfloat16); _check(w, "grouped weights", torch.bfloat16); _check(tile_group, "tile list", torch.int32)
+    G, N, K = w.shape
+    M = x.shape[0]
+    cols = N // 2 if act is not None else N
+    if x.shape[1] != K or tuple(y.shape) != (M, cols) or tile_group.numel() * GROUP_TILE < M:
+        raise KernelError(f"gemm_tcgen05_grouped shapes do not fit: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
+    _call("lb_gemm_tcgen05_grouped", y.data_ptr(), dtype_code(y.dtype), x.data_ptr(), w.data_ptr(), M, N, K, K, cols,
+          (1 + GATE_ACTS[act]) if act is not None else 0, limit, tile_group.data_ptr(), G, stream)
 
 
 def expert_combine(out: torch.Tensor, y: torch.Tensor, weights: torch.Tensor, place_of: torch.Tensor, stream: int,
