@@ -291,7 +291,7 @@ __global__ void __launch_bounds__(256) expert_gemm_plain_kernel(ExpertGemmParams
 // memory that 16-byte asynchronous copies fill three blocks ahead of the tensor cores (with a few tokens the kernel
 // streams the experts' weights, and the copies in flight are what fills the memory pipe); fragments by ldmatrix from
 // rows padded to 80 bytes.  K a multiple of 8, 16-byte aligned rows.
-constexpr int EM_BM = 64, EM_BN = 128, EM_BK = 32, EM_LD = EM_BK + 8, EM_STAGES = 4;
+constexpr int EM_BM = 64, EM_BK = 32, EM_LD = EM_BK + 8, EM_STAGES = 4;
 
 __device__ __forceinline__ void ex_mma_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -307,11 +307,15 @@ __device__ __forceinline__ void ex_cp_async16(void* dst, const void* src, bool v
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(n) : "memory");
 }
 
-template <bool GATED>
-constexpr int expert_mma_smem() { return EM_STAGES * (EM_BM + (GATED ? 2 : 1) * EM_BN) * EM_LD * 2; }
+template <bool GATED, int BN>
+constexpr int expert_mma_smem() { return EM_STAGES * (EM_BM + (GATED ? 2 : 1) * BN) * EM_LD * 2; }
 
-template <typename TY, bool GATED>
+// BN: output columns of a tile, 128 or 64 (with few places a launch is a stream of weights, and narrower tiles are more
+// CTAs to share it out over the SMs)
+template <typename TY, bool GATED, int BN>
 __global__ void __launch_bounds__(256) expert_gemm_mma_kernel(ExpertGemmParams p) {
+  constexpr int EM_BN = BN;
+  constexpr int NW = BN / 32;                                     // blocks of 8 columns a warp: 4 or 2
   extern __shared__ __align__(16) uint8_t ex_smem[];
   constexpr int NB = GATED ? 2 : 1;
   bf16* As = reinterpret_cast<bf16*>(ex_smem);                    // [stage][BM][LD]
@@ -324,7 +328,7 @@ __global__ void __launch_bounds__(256) expert_gemm_mma_kernel(ExpertGemmParams p
   const int e = m[0], r0 = m[1], r1 = m[2];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t4 = lane & 3;
-  const int wm = (warp & 1) * 32, wn = (warp >> 1) * 32;
+  const int wm = (warp & 1) * 32, wn = (warp >> 1) * (BN / 4);
   const int ncols = GATED ? p.N / 2 : p.N;
   const int n0 = blockIdx.x * EM_BN;
   const bf16* x = (const bf16*)p.x;
@@ -339,8 +343,8 @@ __global__ void __launch_bounds__(256) expert_gemm_mma_kernel(ExpertGemmParams p
   auto load_stage = [&](int st, int k0) {
     ex_cp_async16(As + (st * EM_BM + a_r) * EM_LD + a_c, a_row >= 0 ? x + (size_t)a_row * p.ldx + k0 + a_c : x, a_row >= 0 && k0 + a_c < p.K);
 #pragma unroll
-    for (int it = 0; it < 2; ++it) {
-      const int idx = tid + it * 256, r = idx >> 2, c = (idx & 3) * 8;   // 128 rows x 4 pieces
+    for (int it = 0; it < BN / 64; ++it) {
+      const int idx = tid + it * 256, r = idx >> 2, c = (idx & 3) * 8;   // BN rows x 4 pieces
       const bool ok = n0 + r < ncols && k0 + c < p.K;
       int gr = n0 + r, ur = n0 + r;
       if (GATED) gate_up_rows(p, n0 + r, ncols, gr, ur);
@@ -348,11 +352,11 @@ __global__ void __launch_bounds__(256) expert_gemm_mma_kernel(ExpertGemmParams p
       if (GATED) ex_cp_async16(Bs + ((st * NB + 1) * EM_BN + r) * EM_LD + c, ok ? w + (size_t)ur * p.K + k0 + c : w, ok);
     }
   };
-  float acc[2][4][4], acc2[GATED ? 2 : 1][4][4];
+  float acc[2][NW][4], acc2[GATED ? 2 : 1][NW][4];
 #pragma unroll
   for (int i = 0; i < 2; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < NW; ++j)
 #pragma unroll
       for (int k = 0; k < 4; ++k) { acc[i][j][k] = 0.f; if (GATED) acc2[i][j][k] = 0.f; }
   const int nk = (p.K + EM_BK - 1) / EM_BK;
@@ -378,7 +382,7 @@ __global__ void __launch_bounds__(256) expert_gemm_mma_kernel(ExpertGemmParams p
       for (int mi = 0; mi < 2; ++mi)
         ex_ldmatrix_x4(As + (st * EM_BM + wm + mi * 16 + a_lr) * EM_LD + kk + a_lk, a[mi][0], a[mi][1], a[mi][2], a[mi][3]);
 #pragma unroll
-      for (int nb = 0; nb < 4; nb += 2) {
+      for (int nb = 0; nb < NW; nb += 2) {
         uint32_t b0, b1, b2, b3;
         ex_ldmatrix_x4(Bs + ((st * NB + 0) * EM_BN + wn + nb * 8 + b_lr) * EM_LD + kk + b_lk, b0, b1, b2, b3);
         const uint32_t lo[2] = {b0, b1}, hi[2] = {b2, b3};
@@ -397,7 +401,7 @@ __global__ void __launch_bounds__(256) expert_gemm_mma_kernel(ExpertGemmParams p
 #pragma unroll
   for (int mi = 0; mi < 2; ++mi)
 #pragma unroll
-    for (int nb = 0; nb < 4; ++nb)
+    for (int nb = 0; nb < NW; ++nb)
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         const int place = r0 + wm + mi * 16 + g + 8 * half;
@@ -501,19 +505,30 @@ LB_EXPORT int lb_expert_gemm(void* y, int y_dtype, const void* x, int x_dtype, c
   const int ncols = gated ? N / 2 : N;
   const bool mma = fast && x_dtype == LB_BF16 && w_dtype == LB_BF16 && K % 8 == 0 && ldx % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0;
   if (mma) {
-    dim3 grid((ncols + lb::EM_BN - 1) / lb::EM_BN, max_tiles);
     static bool attr_set = false;
     if (!attr_set) {       // the stages need more shared memory than a launch gets unasked
-      cudaFuncSetAttribute(lb::expert_gemm_mma_kernel<float, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::expert_mma_smem<true>());
-      cudaFuncSetAttribute(lb::expert_gemm_mma_kernel<lb::bf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::expert_mma_smem<true>());
-      cudaFuncSetAttribute(lb::expert_gemm_mma_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::expert_mma_smem<false>());
-      cudaFuncSetAttribute(lb::expert_gemm_mma_kernel<lb::bf16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::expert_mma_smem<false>());
+      cudaFuncSetAttribute(lb::expert_gemm_mma_kernel<float, true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::expert_mma_smem<true, 128>());
+      cudaFuncSetAttribute(lb::expert_gemm_mma_kernel<lb::bf16, true, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::expert_mma_smem<true, 128>());
+      cudaFuncSetAttribute(lb::expert_gemm_mma_kernel<float, false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::expert_mma_smem<false, 128>());
+      cudaFuncSetAttribute(lb::expert_gemm_mma_kernel<lb::bf16, false, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::expert_mma_smem<false, 128>());
+      cudaFuncSetAttribute(lb::expert_gemm_mma_kernel<float, true, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::expert_mma_smem<true, 64>());
+      cudaFuncSetAttribute(lb::expert_gemm_mma_kernel<lb::bf16, true, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, lb::expert_mma_smem<true, 64>());
       attr_set = true;
     }
-    LB_DISPATCH_DTYPE(y_dtype, TY, {
-      if (gated) lb::launch(lb::expert_gemm_mma_kernel<TY, true>, grid, dim3(256), lb::expert_mma_smem<true>(), stream, p);
-      else lb::launch(lb::expert_gemm_mma_kernel<TY, false>, grid, dim3(256), lb::expert_mma_smem<false>(), stream, p);
-    })
+    // few row tiles and a gated product (two weight rows a column): tiles of 64 columns, twice the CTAs for the same weights
+    const bool narrow = gated && (long long)max_tiles * ((ncols + 127) / 128) < 2 * 148;
+    if (narrow) {
+      dim3 grid((ncols + 63) / 64, max_tiles);
+      LB_DISPATCH_DTYPE(y_dtype, TY, {
+        lb::launch(lb::expert_gemm_mma_kernel<TY, true, 64>, grid, dim3(256), lb::expert_mma_smem<true, 64>(), stream, p);
+      })
+    } else {
+      dim3 grid((ncols + 127) / 128, max_tiles);
+      LB_DISPATCH_DTYPE(y_dtype, TY, {
+        if (gated) lb::launch(lb::expert_gemm_mma_kernel<TY, true, 128>, grid, dim3(256), lb::expert_mma_smem<true, 128>(), stream, p);
+        else lb::launch(lb::expert_gemm_mma_kernel<TY, false, 128>, grid, dim3(256), lb::expert_mma_smem<false, 128>(), stream, p);
+      })
+    }
   } else {
     dim3 grid((ncols + lb::EX_BN - 1) / lb::EX_BN, max_tiles);
     LB_DISPATCH_DTYPE(x_dtype, TX, {
