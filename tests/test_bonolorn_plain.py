@@ -136,3 +136,21 @@ def test_model_names_every_tensor_of_its_checkpoint():
         assert specs == {k: tuple(v.shape) for k, v in w.items()}, name
         requests = model.cache_requests()
         assert all(isinstance(r, tuple) and len(r) == 2 for r in requests)
+
+
+def test_the_measurement_configurations_are_valid():
+    """What `bench.py --design bonolorn` builds at its sizes parses as Bonolorn, Riruzen and Qwen3 configurations."""
+    import sys
+
+    from conftest import ROOT
+    sys.path.insert(0, str(ROOT))
+    import bench
+    from lucciola_b200.config import resolve_architecture
+    for size in bench.DESIGN_SIZES.values():
+        cfgs = bench.design_configs(size, 4, 4096)
+        assert set(cfgs) == {"bonolorn", "riruzen", "qwen3"}
+        for name, cfg in cfgs.items():
+            arch = resolve_architecture(cfg)
+            arch.config_from_dict(cfg)
+            cost = bench.design_costs(name, cfg)
+            assert cost["weight_bytes"] > 0 and cost["flops_per_token"] > 0 and cost["attn_flops"](64) > 0
