@@ -67,6 +67,8 @@ struct TcAttnParams {
   const int4* tiles;                        // {first token, tokens, request index, unused}
   int num_q_heads, num_kv_heads, group, page_size, page_shift, window;
   float scale_log2;
+  const float* slopes;                      // optional [num_q_heads]: the score of key j for the query at position i is lowered by
+  float inv_scale;                          // slopes[h] * (i - j); 1 / scale brings that into the raw score's units
   // With gridDim.z > 1 the keys of every work item are cut into gridDim.z ranges of whole blocks, one CTA each; a CTA
   // then leaves its rows unnormalised, with their reference value and sum, for ta_combine_kernel:
   float* part_o;                            // [(item * kv heads + kv head) * ranges + range][TA_PART_ROWS][d] float32
@@ -424,6 +426,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
     const bool row_valid = r < per * G && tok_in_item < ntok;       // (128 - per * G rows of a tile stay unused when G does not divide 128)
     const int row_pos = row_valid ? pos0 + tok_in_item : -1;
     const int row_lo = p.window > 0 ? max(0, row_pos - p.window + 1) : 0;
+    const float row_bias = (p.slopes && row_valid) ? p.slopes[kvh * G + r % G] * p.inv_scale : 0.f;   // this row's head: its distance slope
     const int tile_pos0 = pos0 + t * per;                    // the smallest position among the tile's rows
     float m_ref = -INFINITY, l_run = 0.f;
     bool ok = true;
@@ -441,6 +444,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, TcAttnParams
         ta_tmem_ld64(s_addr + (uint32_t)b * 64u, v);
 #pragma unroll
         for (int j = 0; j < 64; ++j) x[j] = __uint_as_float(v[j]);
+      }
+      if (p.slopes) {                                         // the distance bias, before the maximum is taken
+        const float d0 = (float)(row_pos - kb);
+#pragma unroll
+        for (int j = 0; j < TA_KEYS; ++j) x[j] = fmaf(-row_bias, d0 - (float)j, x[j]);
       }
       if (need_mask) {
 #pragma unroll
@@ -671,7 +679,8 @@ LB_EXPORT int lb_attention_tcgen05(const void* q, void* out, const void* k_cache
                                    const int* block_table, const void* tiles, int num_tiles, int num_tokens,
                                    int num_q_heads, int num_kv_heads, int head_dim, int page_size, int num_pages,
                                    int max_pages, int window, float scale, int key_splits, float* workspace,
-                                   long long workspace_elems, cudaStream_t stream) {
+                                   long long workspace_elems, const float* slopes, cudaStream_t stream) {
+  LB_CHECK_ARG(slopes == nullptr || scale > 0.f, "attention_tcgen05: a distance bias needs a positive scale");
   LB_CHECK_ARG(lb_attention_tcgen05_ok(num_q_heads, num_kv_heads, head_dim, page_size),
                "attention_tcgen05: needs head_dim 128, at most 128 query heads per kv head and a page size among 8, 16, 32, 64, 128 "
                "(got head_dim %d, %d/%d heads, pages of %d)", head_dim, num_q_heads, num_kv_heads, page_size);
@@ -698,6 +707,7 @@ LB_EXPORT int lb_attention_tcgen05(const void* q, void* out, const void* k_cache
   p.out = (lb::bf16*)out; p.k_cache = (const uint8_t*)k_cache; p.v_cache = (const uint8_t*)v_cache; p.positions = positions; p.block_table = block_table; p.max_pages = max_pages;
   p.tiles = (const int4*)tiles; p.num_q_heads = num_q_heads; p.num_kv_heads = num_kv_heads; p.group = group;
   p.page_size = page_size; p.window = window; p.scale_log2 = scale * 1.4426950408889634f;
+  p.slopes = slopes; p.inv_scale = slopes ? 1.f / scale : 0.f;
   p.page_shift = 0;
   while ((1 << p.page_shift) < page_size) ++p.page_shift;
   const int smem = lb::TA_SMEM_BYTES + 1024;

@@ -82,7 +82,7 @@ _SIGNATURES = {
     "lb_attention_flash": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                            c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_longlong, c_int, c_void_p, c_void_p],
     "lb_attention_tcgen05": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong, c_void_p],
+                             c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_longlong, c_void_p, c_void_p],
     "lb_sample": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
 }
 
@@ -895,7 +895,7 @@ def attention_tcgen05_splits(num_tiles: int, num_kv_heads: int, max_span: int, s
 def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       positions: torch.Tensor, block_table: torch.Tensor, tiles: torch.Tensor, num_q_heads: int,
                       num_kv_heads: int, head_dim: int, page_size: int, window: int, scale: float, stream: int,
-                      key_splits: int = 1) -> None:
+                      key_splits: int = 1, slopes: torch.Tensor | None = None) -> None:
     """Attention of portions of prompts on tcgen05 (S and O in tensor memory).  tiles: int32 [n, 4] of
     (first token, tokens, request index, 0) with tokens <= 2 * (128 // (nq // nkv)).  With key_splits > 1 the keys of
     every tile are cut into that many ranges, a CTA each, combined by a second kernel."""
@@ -910,7 +910,7 @@ def attention_tcgen05(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
     _call("lb_attention_tcgen05", q.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
           positions.data_ptr(), block_table.data_ptr(), tiles.data_ptr(), tiles.shape[0], q.shape[0], num_q_heads,
           num_kv_heads, head_dim, page_size, k_cache.shape[0], block_table.shape[1], window, scale, key_splits,
-          _ptr(ws), ws_elems, stream)
+          _ptr(ws), ws_elems, _ptr(slopes), stream)
 
 
 def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step, group: int,
@@ -934,12 +934,11 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
     kinds = ["all"]
     if slopes is not None:
         _check(slopes, "distance slopes", torch.float32)
-    # (the tensor-memory kernel knows no distance bias: with one, portions of prompts go to the mma.sync kernel too)
-    if "big" in meta and slopes is None and attention_tcgen05_ok(q, num_q_heads, num_kv_heads, head_dim, page_size,
+    if "big" in meta and attention_tcgen05_ok(q, num_q_heads, num_kv_heads, head_dim, page_size,
                                               step.block_tables[group].shape[1]):
         attention_tcgen05(q, out, k_cache, v_cache, step.positions, step.block_tables[group], meta["big"],
                           num_q_heads, num_kv_heads, head_dim, page_size, window, scale, stream,
-                          key_splits=attention_tcgen05_splits(meta["big"].shape[0], num_kv_heads, span))
+                          key_splits=attention_tcgen05_splits(meta["big"].shape[0], num_kv_heads, span), slopes=slopes)
         kinds = ["rest"] if "rest" in meta else []
     for kind in kinds:
         tiles = meta[kind]
